@@ -1,0 +1,335 @@
+"""Benchmark of the cdist hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--p 1.0]
+
+One "step" is one full cdist over the headline workload: a[K=1024, M=30000], b[K=1024,
+N=30000], float32, entries N(0,1) from seed 1, out[N, M] (3.6 GB), epilogue on.  The
+default p is 1.0; p = 2.0 and p = 1.3 on the same inputs are measured too and reported
+under "also".  At N > 1 GPUs the output rows are sharded over ranks (fixed total work:
+strong scaling) and the step ends with an all-gather of the row slabs.
+
+Prints ONE JSON line (rank 0):
+  value      difference-ops per second, 3*M*N*K per step, inputs resident on the device
+  e2e        same metric through kermac_b200.HostCdist: pinned host inputs copied in, result
+             copied out to pinned host memory, every step
+  roofline   the cdist kernel against the FP32 pipe peak measured on this device
+  cpu_baseline  torch.cdist float32 on the host cores over a bounded row slab
+`--impl reference` times that CPU arm alone (the reference has no CPU implementation of
+its own; torch.cdist is what its tests and README compare against).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+K_DIM, M_DIM, N_DIM, SEED = 1024, 30000, 30000, 1
+WORKLOAD = "cdist fp32 a[K=1024,M=30000] b[K=1024,N=30000] N(0,1) seed 1, out[N,M], full epilogue"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--p", type=float, default=1.0)
+    ap.add_argument("--m", type=int, default=M_DIM)
+    ap.add_argument("--n", type=int, default=N_DIM)
+    ap.add_argument("--k", type=int, default=K_DIM)
+    ap.add_argument("--no-also", action="store_true", help="skip the p=2 / p=1.3 side measurements")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-rows", type=int, default=512)
+    return ap.parse_args()
+
+
+def make_inputs(m, n, k):
+    g = torch.Generator().manual_seed(SEED)
+    a_store = torch.randn(k, m, generator=g, dtype=torch.float32)
+    b_store = torch.randn(k, n, generator=g, dtype=torch.float32)
+    return a_store, b_store
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.lines = []
+        self.proc = None
+        self.thread = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        busy = [c for c, w in zip(sm, power) if w >= 0.5 * max(power)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "power_w_max": max(power),
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args):
+    """torch.cdist float32 on the host cores, a bounded row slab per step (rank 0 only)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import cpu_baseline
+    a_store, b_store = make_inputs(args.m, args.n, args.k)
+    rows = min(args.cpu_rows, args.n)
+    for _ in range(max(args.warmup, 0)):
+        cpu_baseline.time_cdist_slab(a_store, b_store, args.p, rows=min(rows, 64), repeats=1)
+    times = []
+    for _ in range(args.steps):
+        r = cpu_baseline.time_cdist_slab(a_store, b_store, args.p, rows=rows, repeats=1)
+        times.append(r["seconds"])
+    per_step = sum(times) / len(times)
+    value = 3.0 * args.m * rows * args.k / per_step
+    line = {
+        "impl": "reference", "metric": metric_name(args.p), "value": value, "unit": "diff-ops/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_dict(args, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "diff-ops/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": r["sample"]},
+        "e2e": {"value": value, "unit": "diff-ops/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def metric_name(p):
+    return f"cdist difference-ops/s (3*M*N*K per step), fp32, p={p:g}"
+
+
+def config_dict(args, world):
+    return {"workload": WORKLOAD if (args.m, args.n, args.k) == (M_DIM, N_DIM, K_DIM)
+            else f"cdist fp32 a[K={args.k},M={args.m}] b[K={args.k},N={args.n}] N(0,1) seed 1",
+            "p": args.p, "M": args.m, "N": args.n, "K": args.k,
+            "sharding": "single GPU" if world == 1 else f"output rows N sharded over {world} ranks + all-gather",
+            "l2": "inputs (246 MB) and output (3.6 GB) exceed the 126 MB L2; no flush needed between steps"}
+
+
+def timed_steps(fn, steps, warmup, barrier):
+    """Runs fn() warmup + steps times; returns (total ms of the timed steps on this rank's device)."""
+    for _ in range(warmup):
+        fn()
+    barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return e0.elapsed_time(e1)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: kermac_b200 has no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    import kermac_b200 as kermac
+    from kermac_b200 import _native, dist as kdist
+    from kermac_b200.host import HostCdist
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    M, N, K = args.m, args.n, args.k
+    a_store, b_store = make_inputs(M, N, K)
+    a_dev, b_dev = a_store.to(device), b_store.to(device)
+    a, b = a_dev.t(), b_dev.t()                    # API tensors (M, K), (N, K), m / n contiguous
+    start, stop = kdist.shard_rows(N, rank, world, kdist.ROW_ALIGN)
+    slab = torch.empty((stop - start, M), dtype=torch.float32, device=device)
+    launches = {"n": 0}
+
+    def compute_step(p):
+        def step():
+            if stop > start:
+                kermac.cdist(a, b[start:stop], out=slab.t(), p=p)
+                launches["n"] += 1
+        return step
+
+    def job_step(p):
+        compute = compute_step(p)
+
+        def step():
+            compute()
+            if world > 1:
+                kdist.gather_rows(slab, N, None, kdist.ROW_ALIGN)
+        return step
+
+    ops_total = 3.0 * M * N * K
+    results = {}
+    with ClockSampler(local_rank) as clocks:
+        launches["n"] = 0
+        ms = max_over_ranks(timed_steps(job_step(args.p), args.steps, args.warmup, barrier))
+        timed_launches = launches["n"] - args.warmup
+    ms_per_step = ms / args.steps
+    value = ops_total / (ms_per_step * 1e-3)
+    clock_info = clocks.summary()
+
+    # kernel-only time (no gather) on this rank's slab, for the roofline
+    k_ms = max_over_ranks(timed_steps(compute_step(args.p), args.steps, 1, barrier)) / args.steps
+    slab_ops = 3.0 * M * (stop - start) * K
+
+    line = {
+        "metric": metric_name(args.p), "value": value, "unit": "diff-ops/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_dict(args, world), "clocks": clock_info, "gpu_launches": timed_launches,
+        "compute_only": {"ms_per_step": k_ms, "value": ops_total / (k_ms * 1e-3),
+                         "note": "cdist kernel on this rank's row slab, max over ranks, no gather"},
+    }
+
+    if rank == 0:
+        # FP32 pipe peak of this device at the clocks it runs at now (register-only FMA chains)
+        lane_ops_packed, _ = _native.measure_pipe(1, 8192)
+        lane_ops_scalar, _ = _native.measure_pipe(0, 8192)
+        mufu_ops, _ = _native.measure_pipe(2, 2048)
+        lane_peak = max(lane_ops_packed, lane_ops_scalar)
+        fp32_peak_flops = 2.0 * lane_peak
+        achieved = slab_ops / (k_ms * 1e-3)
+        nominal = 148 * 128 * 2 * 1.965e9
+        line["roofline"] = {
+            "bound": "fp32_simt" if args.p in (1.0, 2.0) else "mufu",
+            "achieved": achieved / 1e12, "peak": fp32_peak_flops / 1e12, "unit": "TFLOP/s (difference-ops)",
+            "frac": achieved / fp32_peak_flops,
+            "peak_source": "measured on this device by kermac_b200_measure_pipe (fma.rn.f32x2 chains), x2 flop per lane-op",
+            "frac_of_nominal_74.45": achieved / nominal,
+            "fma_pipe_lane_utilisation": (2.0 / 3.0) * achieved / lane_peak,
+            "mufu_peak_ops": mufu_ops, "mufu_utilisation": (2.0 / 3.0) * achieved / mufu_ops,
+            "lane_ops_scalar": lane_ops_scalar, "lane_ops_packed": lane_ops_packed,
+            "traffic": None,
+            "hbm_gbs_algorithmic": 4.0 * (M * (stop - start) + K * (M + stop - start)) / (k_ms * 1e-3) / 1e9,
+        }
+
+    if not args.no_also:
+        also = {}
+        for p in (2.0, 1.3):
+            if p == args.p:
+                continue
+            steps = args.steps if p == 2.0 else max(2, args.steps // 3)
+            t = max_over_ranks(timed_steps(compute_step(p), steps, 1, barrier)) / steps
+            also[f"p={p:g}"] = {"ms_per_step": t, "value": ops_total / (t * 1e-3), "unit": "diff-ops/s",
+                                "note": "compute only (no gather)"}
+        line["also"] = also
+
+    if not args.no_e2e:
+        pipe = HostCdist(M, stop - start, K, device=device, slabs=8)
+        a_pin = a_store.pin_memory()
+        b_pin = b_store[:, start:stop].contiguous().pin_memory()
+        out_pin = torch.empty((stop - start, M), dtype=torch.float32).pin_memory()
+        del slab
+        torch.cuda.empty_cache()
+
+        def e2e_step():
+            pipe.run(a_pin, b_pin, out_pin, p=args.p)
+
+        e_steps = max(2, min(args.steps, 5))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(e_steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / e_steps
+        barrier()
+        line["e2e"] = {"value": ops_total / (e_ms * 1e-3), "unit": "diff-ops/s", "ms_per_step": e_ms,
+                       "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes,
+                       "steps": e_steps,
+                       "note": "kermac_b200.host.HostCdist: pinned host a, b in; out[N,M] slab back to pinned host; "
+                               "bytes are per rank"}
+
+    if rank == 0 and not args.no_cpu:
+        from oracle import cpu_baseline
+        line["cpu_baseline"] = cpu_baseline.time_cdist_slab(a_store, b_store, args.p, rows=args.cpu_rows, repeats=3,
+                                                            budget_s=20.0)
+    if rank == 0:
+        assert _native.device_error_flag() == 0, "a bounded wait inside a kernel ran out"
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,256 @@
+// Shared device helpers for the kermac_b200 kernels (sm_100a only).
+//
+// The scalar math helpers restate the approximate-math conventions of the
+// reference's include/kermac_internal_common.cuh:76-192 (sqrt.approx.ftz,
+// ex2.approx.ftz(x * log2 e), ex2(p * lg2 v), copysign-based signum) so results
+// agree with it to rounding.  The packed helpers use the sm_100-only f32x2
+// instructions, which carry two fp32 lane-operations per issue slot.
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "../../include/kermac_b200.h"
+
+namespace km {
+
+typedef unsigned long long u64;
+
+// ---------------------------------------------------------------- scalar math
+__device__ __forceinline__ float sqrt_approx(float v) {
+    float r;
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
+}
+__device__ __forceinline__ float ex2_approx(float v) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
+}
+__device__ __forceinline__ float lg2_approx(float v) {
+    float r;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
+}
+// exp(v) as ex2(v * log2(e)); 0f3FB8AA3B is log2(e) rounded to fp32.
+__device__ __forceinline__ float exp_approx(float v) {
+    float t;
+    asm("mul.ftz.f32 %0, %1, 0f3FB8AA3B;" : "=f"(t) : "f"(v));
+    return ex2_approx(t);
+}
+// v^p for v >= 0 as ex2(p * lg2 v): pow(0, p>0) = 0, pow(0, 0) = NaN.
+__device__ __forceinline__ float pow_approx(float v, float p) {
+    float t = lg2_approx(v);
+    asm("mul.ftz.f32 %0, %0, %1;" : "+f"(t) : "f"(p));
+    return ex2_approx(t);
+}
+
+// ---------------------------------------------------------------- packed f32x2
+__device__ __forceinline__ u64 pack2(float lo, float hi) {
+    u64 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(u64 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ u64 sub2(u64 a, u64 b) {
+    u64 r;
+    asm("sub.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ u64 add2(u64 a, u64 b) {
+    u64 r;
+    asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ u64 mul2(u64 a, u64 b) {
+    u64 r;
+    asm("mul.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) {
+    u64 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// ---------------------------------------------------------------- async copies
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+// 16-byte global->shared copy that reads only `src_bytes` (0..16) bytes and
+// zero-fills the rest of the destination.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// 4-byte global->shared copy; src_bytes 0 zero-fills.
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Reads a hyper-parameter for batch entry l.
+__device__ __forceinline__ float read_hyper(const KmHyper& h, int l) {
+    return h.ptr ? h.ptr[static_cast<long long>(l) * h.batch_stride] : h.value;
+}
+
+// The outer power, epsilon mask and kernel function applied to one accumulated
+// sum, in the order of the reference's epilogue (include/build_a_kernel.cuh:374-427):
+// outer power; values below epsilon become 0 (only when a kernel function is
+// chosen); Laplace exp(-x / bw) or Gaussian exp(-x / (2 bw^2)).
+struct Epilogue {
+    int   outer_power;
+    int   kernel_type;
+    float p_outer;
+    float neg_gamma;   // -1/bw (Laplace) or -1/(2 bw^2) (Gaussian)
+    float epsilon;
+
+    __device__ __forceinline__ float operator()(float acc) const {
+        switch (outer_power) {
+            case KM_POW_ABS: acc = fabsf(acc); break;
+            case KM_POW_SQUARE: acc = acc * acc; break;
+            case KM_POW_SQRT: acc = sqrt_approx(acc); break;
+            case KM_POW_POW: acc = pow_approx(acc, p_outer); break;
+            default: break;
+        }
+        if (kernel_type != KM_KERNEL_NONE) {
+            if (acc < epsilon) acc = 0.0f;
+            acc = exp_approx(acc * neg_gamma);
+        }
+        return acc;
+    }
+};
+
+__device__ __forceinline__ Epilogue make_epilogue(int outer_power, int kernel_type, const KmHyper& p_outer,
+                                                  const KmHyper& bandwidth, float epsilon, int l) {
+    Epilogue e;
+    e.outer_power = outer_power;
+    e.kernel_type = kernel_type;
+    e.p_outer     = (outer_power == KM_POW_POW) ? read_hyper(p_outer, l) : 0.0f;
+    e.epsilon     = epsilon;
+    e.neg_gamma   = 0.0f;
+    if (kernel_type != KM_KERNEL_NONE) {
+        float bw    = read_hyper(bandwidth, l);
+        float gamma = (kernel_type == KM_KERNEL_LAPLACE) ? (1.0f / bw) : (1.0f / (2.0f * bw * bw));
+        e.neg_gamma = -gamma;
+    }
+    return e;
+}
+
+// Inner-step identifiers: operator x power of the reference's template pair
+// (InnerOperator, PowerType inner), include/build_a_kernel.cuh:344-366.
+enum InnerId {
+    IN_DIFF_ABS = 0,
+    IN_DIFF_SQUARE,
+    IN_DIFF_POW,
+    IN_DIFF_NOOP,
+    IN_DIFF_SQRT,
+    IN_DOT_NOOP,
+    IN_DOT_ABS,
+    IN_DOT_SQUARE,
+    IN_DOT_SQRT,
+    IN_DOT_POW,
+    IN_COUNT
+};
+
+__host__ __device__ inline int inner_id(int op, int power) {
+    if (op == KM_INNER_DIFF) {
+        switch (power) {
+            case KM_POW_ABS: return IN_DIFF_ABS;
+            case KM_POW_SQUARE: return IN_DIFF_SQUARE;
+            case KM_POW_POW: return IN_DIFF_POW;
+            case KM_POW_NOOP: return IN_DIFF_NOOP;
+            case KM_POW_SQRT: return IN_DIFF_SQRT;
+        }
+    } else if (op == KM_INNER_DOT) {
+        switch (power) {
+            case KM_POW_NOOP: return IN_DOT_NOOP;
+            case KM_POW_ABS: return IN_DOT_ABS;
+            case KM_POW_SQUARE: return IN_DOT_SQUARE;
+            case KM_POW_SQRT: return IN_DOT_SQRT;
+            case KM_POW_POW: return IN_DOT_POW;
+        }
+    }
+    return -1;
+}
+
+// One k step of an 8 (rows of the pair-packed operand) x 8 register block.
+//   ap[4]  : the 8 values of the m-side operand as 4 packed pairs (m, m+1)
+//   bv[8]  : the 8 values of the n-side operand
+//   acc    : acc[n][mp] packed pair of accumulators for (m = 2 mp, 2 mp + 1)
+// `sgn` is +1 normally and -1 when the launcher exchanged the two operands (so
+// that signed inner steps still see b - a).
+template <int INNER>
+__device__ __forceinline__ void inner_block(u64 (&acc)[8][4], const u64 (&ap)[4], const float (&bv)[8], float p_inner,
+                                            float sgn) {
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        const u64 bd = pack2(bv[n], bv[n]);
+#pragma unroll
+        for (int mp = 0; mp < 4; ++mp) {
+            if constexpr (INNER == IN_DIFF_SQUARE) {
+                const u64 d = sub2(bd, ap[mp]);
+                acc[n][mp]  = fma2(d, d, acc[n][mp]);
+            } else if constexpr (INNER == IN_DOT_NOOP) {
+                acc[n][mp] = fma2(bd, ap[mp], acc[n][mp]);
+            } else {
+                const u64 d = (INNER >= IN_DOT_NOOP) ? mul2(bd, ap[mp]) : sub2(bd, ap[mp]);
+                float d0, d1, a0, a1;
+                unpack2(d, d0, d1);
+                unpack2(acc[n][mp], a0, a1);
+                if constexpr (INNER == IN_DIFF_ABS || INNER == IN_DOT_ABS) {
+                    a0 += fabsf(d0);
+                    a1 += fabsf(d1);
+                } else if constexpr (INNER == IN_DIFF_POW || INNER == IN_DOT_POW) {
+                    a0 += pow_approx(fabsf(d0), p_inner);
+                    a1 += pow_approx(fabsf(d1), p_inner);
+                } else if constexpr (INNER == IN_DIFF_NOOP) {
+                    a0 += d0;
+                    a1 += d1;
+                } else if constexpr (INNER == IN_DIFF_SQRT) {
+                    a0 += sqrt_approx(d0 * sgn);
+                    a1 += sqrt_approx(d1 * sgn);
+                } else if constexpr (INNER == IN_DOT_SQUARE) {
+                    a0 = fmaf(d0, d0, a0);
+                    a1 = fmaf(d1, d1, a1);
+                } else if constexpr (INNER == IN_DOT_SQRT) {
+                    a0 += sqrt_approx(d0);
+                    a1 += sqrt_approx(d1);
+                }
+                acc[n][mp] = pack2(a0, a1);
+            }
+        }
+    }
+}
+
+// Consumes one staged k slab ([BK][PITCH] floats per operand, tile dimension
+// contiguous) for a thread whose 8 x 8 block reads the m-side at sa + {0, 32} and
+// the n-side at sb + {0, 16}.  Only the first `kvalid` k rows are used, so a partial
+// last slab contributes exactly the rows that exist.
+template <int INNER, int BK, int PITCH>
+__device__ __forceinline__ void consume_slab(u64 (&acc)[8][4], const float* sa, const float* sb, int kvalid,
+                                             float p_inner, float sgn) {
+    auto step = [&](int kk) {
+        const ulonglong2 a0 = *reinterpret_cast<const ulonglong2*>(sa + kk * PITCH);
+        const ulonglong2 a1 = *reinterpret_cast<const ulonglong2*>(sa + kk * PITCH + 32);
+        const float4     b0 = *reinterpret_cast<const float4*>(sb + kk * PITCH);
+        const float4     b1 = *reinterpret_cast<const float4*>(sb + kk * PITCH + 16);
+        const u64   ap[4] = {a0.x, a0.y, a1.x, a1.y};
+        const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        inner_block<INNER>(acc, ap, bv, p_inner, sgn);
+    };
+    if (kvalid >= BK) {
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) step(kk);
+    } else {
+#pragma unroll 1
+        for (int kk = 0; kk < kvalid; ++kk) step(kk);
+    }
+}
+
+}  // namespace km

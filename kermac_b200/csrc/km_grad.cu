@@ -1,0 +1,373 @@
+// kermac_b200_cdist_grad: the p-norm gradient contraction
+//   out[l, o, n, m] = sum_k c[l, o, k] * a[l, k, m] * g(d[l, n, m] - b[l, n, k])
+// restating what the reference's kernel_cute_p_norm_kernel_gradient computes
+// (include/p_norm_gradient.cuh:22-405) with a different work decomposition:
+//   - a thread block owns a 64 (m) x TN (n) tile for up to OT output channels, with
+//     OT chosen from {1, 2, 4, 8, 16} to fit O (the reference always spends 32);
+//   - the weight w = a * g(diff) is formed once per (m, n, k) and reused for every
+//     channel; for p = 1 the sign is applied with one bit operation on a;
+//   - differences, weights and channel FMAs run on packed pairs along m;
+//   - the contracted k range can be split over several thread blocks, whose partial
+//     tiles go to caller-provided scratch and are summed in a fixed order by a
+//     second kernel, so results do not depend on scheduling.
+#include "km_common.cuh"
+#include "km_host.h"
+
+namespace km {
+namespace {
+
+constexpr int G_THREADS = 256;
+constexpr int G_TM      = 64;
+constexpr int G_BK      = 16;
+constexpr int G_STAGES  = 3;
+
+struct GradParams {
+    int M, N, O, K, L;
+    const float* A; long long lda, a_sl;
+    const float* B; long long ldb, b_sl;
+    const float* C; long long ldc, c_sl;
+    const float* D; long long ldd, d_sl;
+    float*       E; long long e_sn, e_so, e_sl;   // destination (out, or scratch when split)
+    KmHyper p;
+    int tiles_m, tiles_n, o_chunks, splits;
+    int k_per_split;                                // multiple of G_BK
+    long long split_stride;                         // elements between partial results of consecutive splits
+    int a_vec, e_vec;
+};
+
+__device__ __forceinline__ u64 flip_sign2(u64 a, u64 diff) {
+    // a with the sign bit of diff xor-ed in, lane-wise: copysign(1, diff) * a
+    return a ^ (diff & 0x8000000080000000ull);
+}
+
+template <int NORM, int OT, int NT>
+__global__ void __launch_bounds__(G_THREADS, 2) grad_kernel(const __grid_constant__ GradParams p) {
+    constexpr int TN      = 16 * NT;
+    constexpr int PITCH_A = G_TM + 4;
+    constexpr int PITCH_B = TN + 4;
+    constexpr int PITCH_C = (OT < 4 ? 4 : OT);
+    constexpr int STAGE_FLOATS = G_BK * (PITCH_A + PITCH_B + PITCH_C);
+    __shared__ __align__(16) float smem[G_STAGES * STAGE_FLOATS];
+
+    const int tid = threadIdx.x;
+    const int tmi = tid & 15, tni = tid >> 4;
+
+    int bx          = blockIdx.x;
+    const int split = bx % p.splits;  bx /= p.splits;
+    const int tm    = bx % p.tiles_m; bx /= p.tiles_m;
+    const int tn    = bx;
+    const int oc    = blockIdx.y;
+    const int l     = blockIdx.z;
+    const int m0 = tm * G_TM, n0 = tn * TN, o0 = oc * OT;
+
+    const int k_begin = split * p.k_per_split;
+    const int k_end   = min(p.K, k_begin + p.k_per_split);
+    const int ktiles  = (k_end > k_begin) ? (k_end - k_begin + G_BK - 1) / G_BK : 0;
+
+    const float* A = p.A + (long long)l * p.a_sl + m0;
+    const float* B = p.B + (long long)l * p.b_sl + (long long)n0 * p.ldb;
+    const float* C = p.C + (long long)l * p.c_sl + (long long)o0 * p.ldc;
+    const float* D = p.D + (long long)l * p.d_sl;
+
+    float pm1 = 0.0f;
+    if (NORM == KM_NORM_P) pm1 = read_hyper(p.p, l) - 1.0f;
+
+    // d values of this thread: rows n0 + tni * NT + j, columns m0 + tmi * 4 + {0..3}
+    u64 dv[NT][2];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const int n = n0 + tni * NT + j;
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int m = m0 + tmi * 4 + e;
+            v[e]        = (n < p.N && m < p.M) ? D[(long long)n * p.ldd + m] : 0.0f;
+        }
+        dv[j][0] = pack2(v[0], v[1]);
+        dv[j][1] = pack2(v[2], v[3]);
+    }
+
+    u64 acc[NT][OT][2];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int o = 0; o < OT; ++o) acc[j][o][0] = acc[j][o][1] = 0ull;
+
+    auto stage = [&](int s, int kt) {
+        float* sa = smem + s * STAGE_FLOATS;
+        float* sb = sa + G_BK * PITCH_A;
+        float* sc = sb + G_BK * PITCH_B;
+        const int k0 = k_begin + kt * G_BK;
+        if (p.a_vec) {
+            // 16 k rows x 16 chunks of 4 m
+            const int kk = tid >> 4, t = (tid & 15) << 2, gk = k0 + kk;
+            int valid = min(4, p.M - m0 - t);
+            valid     = (gk < k_end && valid > 0) ? valid : 0;
+            cp_async_16(smem_u32(sa + kk * PITCH_A + t), valid ? A + (long long)gk * p.lda + t : p.A, valid * 4);
+        } else {
+#pragma unroll
+            for (int i = 0; i < (G_BK * G_TM) / G_THREADS; ++i) {
+                const int idx = tid + i * G_THREADS;
+                const int t = idx & (G_TM - 1), kk = idx >> 6, gk = k0 + kk;
+                const bool ok = gk < k_end && (m0 + t) < p.M;
+                cp_async_4(smem_u32(sa + kk * PITCH_A + t), ok ? A + (long long)gk * p.lda + t : p.A, ok ? 4 : 0);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < (G_BK * TN + G_THREADS - 1) / G_THREADS; ++i) {
+            const int idx = tid + i * G_THREADS;
+            if (idx < G_BK * TN) {
+                const int kk = idx & (G_BK - 1), t = idx >> 4, gk = k0 + kk;
+                const bool ok = gk < k_end && (n0 + t) < p.N;
+                cp_async_4(smem_u32(sb + kk * PITCH_B + t), ok ? B + (long long)t * p.ldb + gk : p.B, ok ? 4 : 0);
+            }
+        }
+        if (tid < G_BK * OT) {
+            const int kk = tid & (G_BK - 1), t = tid >> 4, gk = k0 + kk;
+            const bool ok = gk < k_end && (o0 + t) < p.O;
+            cp_async_4(smem_u32(sc + kk * PITCH_C + t), ok ? C + (long long)t * p.ldc + gk : p.C, ok ? 4 : 0);
+        }
+    };
+
+    auto step = [&](const float* sa, const float* sb, const float* sc, int kk) {
+        const ulonglong2 a4 = *reinterpret_cast<const ulonglong2*>(sa + kk * PITCH_A + tmi * 4);
+        const u64 av[2]     = {a4.x, a4.y};
+        float bv[NT];
+#pragma unroll
+        for (int j = 0; j < NT; ++j) bv[j] = sb[kk * PITCH_B + tni * NT + j];
+        u64 cd[OT];
+#pragma unroll
+        for (int o = 0; o < OT; ++o) {
+            const float cv = sc[kk * PITCH_C + o];
+            cd[o]          = pack2(cv, cv);
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const u64 bd = pack2(bv[j], bv[j]);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const u64 diff = sub2(dv[j][h], bd);
+                u64 w;
+                if constexpr (NORM == KM_NORM_L1) {
+                    w = flip_sign2(av[h], diff);
+                } else if constexpr (NORM == KM_NORM_L2) {
+                    w = mul2(av[h], diff);
+                } else {
+                    float d0, d1;
+                    unpack2(diff, d0, d1);
+                    const float g0 = copysignf(pow_approx(fabsf(d0), pm1), d0);
+                    const float g1 = copysignf(pow_approx(fabsf(d1), pm1), d1);
+                    w              = mul2(av[h], pack2(g0, g1));
+                }
+#pragma unroll
+                for (int o = 0; o < OT; ++o) acc[j][o][h] = fma2(cd[o], w, acc[j][o][h]);
+            }
+        }
+    };
+
+#pragma unroll
+    for (int s = 0; s < G_STAGES - 1; ++s) {
+        if (s < ktiles) stage(s, s);
+        cp_async_commit();
+    }
+    for (int kt = 0; kt < ktiles; ++kt) {
+        cp_async_wait<G_STAGES - 2>();
+        __syncthreads();
+        const int nk = kt + G_STAGES - 1;
+        if (nk < ktiles) stage(nk % G_STAGES, nk);
+        cp_async_commit();
+        const float* sa = smem + (kt % G_STAGES) * STAGE_FLOATS;
+        const float* sb = sa + G_BK * PITCH_A;
+        const float* sc = sb + G_BK * PITCH_B;
+        const int kvalid = k_end - (k_begin + kt * G_BK);
+        if (kvalid >= G_BK) {
+#pragma unroll
+            for (int kk = 0; kk < G_BK; ++kk) step(sa, sb, sc, kk);
+        } else {
+#pragma unroll 1
+            for (int kk = 0; kk < kvalid; ++kk) step(sa, sb, sc, kk);
+        }
+    }
+    cp_async_wait<0>();
+
+    float* E = p.E + (long long)split * p.split_stride + (long long)l * p.e_sl;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const int n = n0 + tni * NT + j;
+        if (n >= p.N) continue;
+#pragma unroll
+        for (int o = 0; o < OT; ++o) {
+            if (o0 + o >= p.O) continue;
+            float* row = E + (long long)(o0 + o) * p.e_so + (long long)n * p.e_sn;
+            const int m = m0 + tmi * 4;
+            float v[4];
+            unpack2(acc[j][o][0], v[0], v[1]);
+            unpack2(acc[j][o][1], v[2], v[3]);
+            if (p.e_vec && m + 3 < p.M) {
+                *reinterpret_cast<float4*>(row + m) = make_float4(v[0], v[1], v[2], v[3]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (m + e < p.M) row[m + e] = v[e];
+            }
+        }
+    }
+}
+
+// out[l][o][n][m] = sum over splits of partial[split][l][o][n][m] (dense partials).
+__global__ void __launch_bounds__(256) grad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                                          int M, int N, int O, int L, int splits, long long split_stride,
+                                                          long long o_sn, long long o_so, long long o_sl) {
+    const long long total = (long long)L * O * N * M;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        float s = 0.0f;
+        for (int sp = 0; sp < splits; ++sp) s += partial[sp * split_stride + i];
+        long long r = i;
+        const int m = (int)(r % M); r /= M;
+        const int n = (int)(r % N); r /= N;
+        const int o = (int)(r % O); r /= O;
+        const int l = (int)r;
+        out[l * o_sl + o * o_so + n * o_sn + m] = s;
+    }
+}
+
+typedef void (*GradFn)(const GradParams);
+
+template <int NORM>
+GradFn grad_fn_for(int ot) {
+    switch (ot) {
+        case 1: return grad_kernel<NORM, 1, 4>;
+        case 2: return grad_kernel<NORM, 2, 4>;
+        case 4: return grad_kernel<NORM, 4, 4>;
+        case 8: return grad_kernel<NORM, 8, 2>;
+        default: return grad_kernel<NORM, 16, 1>;
+    }
+}
+int nt_for(int ot) { return ot <= 4 ? 4 : (ot == 8 ? 2 : 1); }
+
+struct GradPlan {
+    GradParams p;
+    int ot, nt;
+    int splits_wanted;
+    long long partial_elems;   // elements of one dense partial result
+};
+
+int make_grad_plan(const KmGradArgs* a, GradPlan* plan) {
+    if (!a) return fail(KM_ERR_NULL_POINTER, "args is NULL");
+    if (a->m < 0 || a->n < 0 || a->o < 0 || a->k < 0 || a->l < 1)
+        return fail(KM_ERR_BAD_SHAPE, "bad extents m=%d n=%d o=%d k=%d l=%d", a->m, a->n, a->o, a->k, a->l);
+    if (a->l > 65535) return fail(KM_ERR_TOO_LARGE, "at most 65535 batch entries per call");
+    const bool empty = (a->m == 0 || a->n == 0 || a->o == 0);
+    if (!empty && (!a->out || !a->d || (a->k > 0 && (!a->a || !a->b || !a->c))))
+        return fail(KM_ERR_NULL_POINTER, "a, b, c, d and out must be device pointers");
+    if (a->norm_type < KM_NORM_L1 || a->norm_type > KM_NORM_P)
+        return fail(KM_ERR_BAD_ENUM, "norm_type %d is not a KmNormType", a->norm_type);
+    if ((a->k > 1 && a->lda < a->m) || (a->n > 1 && a->ldb < a->k) || (a->o > 1 && a->ldc < a->k) ||
+        (a->n > 1 && a->ldd < a->m) || (a->n > 1 && a->out_stride_n < a->m))
+        return fail(KM_ERR_BAD_STRIDE, "a row pitch is smaller than the row it spans");
+    if (a->a_stride_l < 0 || a->b_stride_l < 0 || a->c_stride_l < 0 || a->d_stride_l < 0 || a->out_stride_l < 0 ||
+        a->out_stride_o < 0)
+        return fail(KM_ERR_BAD_STRIDE, "strides must be non-negative");
+    if (a->l > 1 && a->out_stride_l == 0) return fail(KM_ERR_BAD_STRIDE, "out cannot be broadcast over the batch");
+    if (!hyper_ok(a->p)) return fail(KM_ERR_BAD_HYPERPARAM, "p needs a non-negative batch stride");
+    if (a->split_k < 0) return fail(KM_ERR_BAD_SHAPE, "split_k must be >= 0");
+
+    GradParams& p = plan->p;
+    p.M = a->m; p.N = a->n; p.O = a->o; p.K = a->k; p.L = a->l;
+    p.A = a->a; p.lda = a->lda; p.a_sl = a->a_stride_l;
+    p.B = a->b; p.ldb = a->ldb; p.b_sl = a->b_stride_l;
+    p.C = a->c; p.ldc = a->ldc; p.c_sl = a->c_stride_l;
+    p.D = a->d; p.ldd = a->ldd; p.d_sl = a->d_stride_l;
+    p.p = a->p;
+    int ot = 1;
+    while (ot < a->o && ot < 16) ot *= 2;
+    plan->ot = ot;
+    plan->nt = nt_for(ot);
+    p.tiles_m  = (int)ceil_div_ll(p.M, G_TM);
+    p.tiles_n  = (int)ceil_div_ll(p.N, 16 * plan->nt);
+    p.o_chunks = (int)ceil_div_ll(p.O > 0 ? p.O : 1, ot);
+    p.a_vec    = aligned16(p.A) && p.lda % 4 == 0 && p.a_sl % 4 == 0;
+    if ((long long)p.tiles_m * p.tiles_n > (1LL << 26)) return fail(KM_ERR_TOO_LARGE, "too many output tiles");
+    if (p.o_chunks > 65535) return fail(KM_ERR_TOO_LARGE, "too many output channels");
+
+    // Preferred k split: enough thread blocks for ~2 waves of 2 blocks per SM, at
+    // least 8 slabs of k per block.
+    const long long blocks = (long long)p.tiles_m * p.tiles_n * p.o_chunks * p.L;
+    const long long target = 4LL * sm_count();
+    int want = 1;
+    if (blocks < target) {
+        want = (int)ceil_div_ll(target, blocks > 0 ? blocks : 1);
+        const int max_by_k = (int)(p.K / (8 * G_BK));
+        if (want > max_by_k) want = max_by_k;
+        if (want > 64) want = 64;
+        if (want < 1) want = 1;
+    }
+    plan->splits_wanted = want;
+    plan->partial_elems = (long long)p.L * p.O * p.N * p.M;
+    return 0;
+}
+
+}  // namespace
+}  // namespace km
+
+extern "C" int64_t kermac_b200_cdist_grad_scratch_bytes(const KmGradArgs* args) {
+    using namespace km;
+    GradPlan plan;
+    if (make_grad_plan(args, &plan)) return 0;
+    int splits = args->split_k > 0 ? args->split_k : plan.splits_wanted;
+    if (splits <= 1) return 0;
+    return (int64_t)splits * plan.partial_elems * 4;
+}
+
+extern "C" int kermac_b200_cdist_grad(const KmGradArgs* args, void* stream) {
+    using namespace km;
+    GradPlan plan;
+    if (int rc = make_grad_plan(args, &plan)) return rc;
+    GradParams& p = plan.p;
+    if (p.M == 0 || p.N == 0 || p.O == 0) return 0;
+    if (int rc = require_sm100()) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    int splits = args->split_k > 0 ? args->split_k : plan.splits_wanted;
+    if (splits > 1) {
+        const int64_t need = (int64_t)splits * plan.partial_elems * 4;
+        if (!args->scratch || args->scratch_bytes < need) {
+            if (args->split_k > 1)
+                return fail(KM_ERR_BAD_SHAPE, "split_k=%d needs %lld bytes of scratch, got %lld", splits, (long long)need,
+                            (long long)(args->scratch ? args->scratch_bytes : 0));
+            splits = 1;   // automatic mode falls back to a single pass
+        }
+    }
+    int slabs       = (int)ceil_div_ll(p.K > 0 ? p.K : 1, G_BK);
+    p.k_per_split   = (int)ceil_div_ll(slabs, splits) * G_BK;
+    splits          = (int)ceil_div_ll(p.K > 0 ? p.K : 1, p.k_per_split);
+    p.splits        = splits;
+    if (splits > 1) {
+        p.E = static_cast<float*>(args->scratch);
+        p.e_sn = p.M; p.e_so = (long long)p.N * p.M; p.e_sl = (long long)p.O * p.N * p.M;
+        p.split_stride = plan.partial_elems;
+        p.e_vec = aligned16(p.E) && p.M % 4 == 0;
+    } else {
+        p.E = args->out;
+        p.e_sn = args->out_stride_n; p.e_so = args->out_stride_o; p.e_sl = args->out_stride_l;
+        p.split_stride = 0;
+        p.e_vec = aligned16(p.E) && p.e_sn % 4 == 0 && p.e_so % 4 == 0 && p.e_sl % 4 == 0;
+    }
+    GradFn fn = nullptr;
+    switch (args->norm_type) {
+        case KM_NORM_L1: fn = grad_fn_for<KM_NORM_L1>(plan.ot); break;
+        case KM_NORM_L2: fn = grad_fn_for<KM_NORM_L2>(plan.ot); break;
+        default: fn = grad_fn_for<KM_NORM_P>(plan.ot); break;
+    }
+    dim3 grid((unsigned)((long long)p.tiles_m * p.tiles_n * splits), (unsigned)p.o_chunks, (unsigned)p.L);
+    fn<<<grid, G_THREADS, 0, st>>>(p);
+    if (int rc = cuda_status(cudaGetLastError(), "launch of grad_kernel")) return rc;
+    if (splits > 1) {
+        const long long total = plan.partial_elems;
+        int blocks = (int)(ceil_div_ll(total, 256) < 4LL * sm_count() ? ceil_div_ll(total, 256) : 4LL * sm_count());
+        grad_reduce_kernel<<<blocks, 256, 0, st>>>(p.E, args->out, p.M, p.N, p.O, p.L, splits, plan.partial_elems,
+                                                   args->out_stride_n, args->out_stride_o, args->out_stride_l);
+        if (int rc = cuda_status(cudaGetLastError(), "launch of grad_reduce_kernel")) return rc;
+    }
+    return 0;
+}

@@ -1,0 +1,329 @@
+"""GPU parity of cdist / run_kernel against the float64 CPU oracle, through the C-ABI.
+
+Tolerances (max relative error, oracle/kermac_oracle.py:rel_err_nonneg): 1e-5 for
+p in {1, 2}, 5e-5 for fractional p and for kernel-function epilogues.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import kermac_b200 as kermac
+from kermac_b200 import _native
+from oracle import kermac_oracle as ko
+
+pytestmark = pytest.mark.gpu
+
+TOL_EXACT = 1e-5
+TOL_FRAC = 5e-5
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def tol_for(p):
+    return TOL_EXACT if p in (1.0, 2.0) else TOL_FRAC
+
+
+def gen(shape, seed, dist="randn"):
+    g = torch.Generator().manual_seed(seed)
+    if dist == "randn":
+        return torch.randn(*shape, generator=g, dtype=torch.float32)
+    if dist == "rand":
+        return torch.rand(*shape, generator=g, dtype=torch.float32)
+    return 2.0 * torch.rand(*shape, generator=g, dtype=torch.float32) - 1.0
+
+
+def col_major(t):
+    """Same values, storage transposed: shape (..., R, C) with strides (..., 1, R)."""
+    return t.transpose(-1, -2).contiguous().transpose(-1, -2)
+
+
+@pytest.fixture(autouse=True)
+def no_expired_waits():
+    yield
+    assert _native.device_error_flag() == 0, "a bounded wait inside a kernel ran out"
+
+
+# ------------------------------------------------------------------ headline configs
+def test_config1_full_check_p2_uniform_inputs():
+    # a[K=64, M=2048], b[K=64, N=2048] ~ U(0,1) seed 0, out[N, M]; whole output vs the oracle
+    g = torch.Generator().manual_seed(0)
+    a_store = torch.rand(64, 2048, generator=g)
+    b_store = torch.rand(64, 2048, generator=g)
+    a, b = a_store.t().cuda(), b_store.t().cuda()
+    out = torch.empty(2048, 2048, device="cuda").t()
+    got = kermac.cdist(a, b, out=out, p=2.0)
+    assert got is out
+    ref = ko.cdist_ref(a_store.t(), b_store.t(), p=2.0)[0]
+    assert ko.rel_err_nonneg(got, ref) < TOL_EXACT
+    assert "variant=tma" in _describe(a, b, out, 2.0)
+
+
+def _describe(a, b, out, p):
+    buf = []
+    import builtins
+    real_print = builtins.print
+    builtins.print = lambda *x, **k: buf.append(" ".join(map(str, x)))
+    try:
+        kermac.cdist(a, b, out=out, p=p, debug=True)
+    finally:
+        builtins.print = real_print
+    return "\n".join(buf)
+
+
+@pytest.mark.parametrize("p", [1.0, 1.3, 2.0])
+def test_golden_vectors(p):
+    z = np.load(os.path.join(GOLDEN, "cdist_small.npz"))
+    a, b = torch.from_numpy(z["a"]).cuda(), torch.from_numpy(z["b"]).cuda()
+    got = kermac.cdist(a, b, p=p)
+    assert ko.rel_err_nonneg(got, torch.from_numpy(z[f"cdist_p{p}"])) < tol_for(p)
+
+
+# ------------------------------------------------------------------ layouts (the reference's test matrix)
+@pytest.mark.parametrize("p", [1.0, 1.3, 2.0])
+@pytest.mark.parametrize("a_col", [False, True])
+@pytest.mark.parametrize("b_col", [False, True])
+@pytest.mark.parametrize("c_col", [False, True])
+def test_all_majorness_combinations(p, a_col, b_col, c_col):
+    # L=2, M=N=1000, K=64 as tests/test_cdist.py:10-13 of the reference; a 1000-wide pitch is
+    # 16-byte aligned, so column-major operands take the vector paths
+    L, M, N, K = 2, 1000, 1000, 64
+    a_h, b_h = gen((L, M, K), 11), gen((L, N, K), 12)
+    a = col_major(a_h).cuda() if a_col else a_h.cuda()
+    b = col_major(b_h).cuda() if b_col else b_h.cuda()
+    out = torch.empty(L, N, M, device="cuda").permute(0, 2, 1) if c_col else torch.empty(L, M, N, device="cuda")
+    for try_to_align in (False, True):
+        out.fill_(-1.0)
+        got = kermac.cdist(a, b, out=out, p=p, try_to_align=try_to_align)
+        assert got is out
+        assert ko.rel_err_nonneg(got, ko.cdist_ref(a_h, b_h, p=p)) < tol_for(p)
+
+
+@pytest.mark.parametrize("variant", ["cpasync", "tma"])
+@pytest.mark.parametrize("p", [1.0, 1.3, 2.0])
+def test_both_variants_on_aligned_column_major(variant, p, monkeypatch):
+    monkeypatch.setenv("KERMAC_B200_VARIANT", variant)
+    M, N, K = 384, 260, 100            # K not a multiple of the slab, N not a multiple of the tile
+    a_h, b_h = gen((M, K), 21), gen((N, K), 22)
+    a, b = col_major(a_h).cuda(), col_major(b_h).cuda()
+    got = kermac.cdist(a, b, p=p)
+    assert ko.rel_err_nonneg(got, ko.cdist_ref(a_h, b_h, p=p)) < tol_for(p)
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1), (3, 5, 2), (31, 33, 7), (127, 129, 17), (129, 127, 33), (257, 130, 48),
+                                   (130, 257, 1), (5, 300, 130)])
+@pytest.mark.parametrize("p", [1.0, 2.0, 1.3])
+def test_odd_shapes_every_layout(shape, p):
+    M, N, K = shape
+    a_h, b_h = gen((M, K), 31), gen((N, K), 32)
+    ref = ko.cdist_ref(a_h, b_h, p=p)[0]
+    for a in (a_h.cuda(), col_major(a_h).cuda()):
+        for b in (b_h.cuda(), col_major(b_h).cuda()):
+            for out in (torch.empty(M, N, device="cuda"), torch.empty(N, M, device="cuda").t()):
+                got = kermac.cdist(a, b, out=out, p=p)
+                assert ko.rel_err_nonneg(got, ref) < tol_for(p), (a.stride(), b.stride(), out.stride())
+
+
+def test_unaligned_views_and_padded_pitches():
+    # base pointers off by one float and pitches that are not multiples of 4
+    M, N, K = 200, 150, 40
+    big_a = gen((K + 3, M + 7), 41).cuda()
+    big_b = gen((K + 3, N + 5), 42).cuda()
+    a = big_a[1:K + 1, 1:M + 1].t()          # (M, K) strides (1, M+7), pointer offset by odd floats
+    b = big_b[2:K + 2, 3:N + 3].t()
+    big_out = torch.full((N + 2, M + 3), -7.0, device="cuda")
+    out = big_out[1:N + 1, 1:M + 1].t()      # (M, N) with m contiguous, unaligned
+    got = kermac.cdist(a, b, out=out, p=2.0)
+    ref = ko.cdist_ref(a.cpu(), b.cpu(), p=2.0)[0]
+    assert ko.rel_err_nonneg(got, ref) < TOL_EXACT
+    # nothing outside the view was written
+    assert float(big_out[0].max()) == -7.0 and float(big_out[-1].max()) == -7.0
+    assert float(big_out[:, 0].max()) == -7.0 and float(big_out[:, M + 1:].max()) == -7.0
+
+
+def test_output_padding_is_untouched_on_the_tma_path():
+    M, N, K = 250, 190, 64
+    a_h, b_h = gen((M, K), 43), gen((N, K), 44)
+    a, b = col_major(a_h).cuda(), col_major(b_h).cuda()
+    big_out = torch.full((N + 4, M + 6), -7.0, device="cuda")     # pitch M+6 = 256: aligned rows
+    out = big_out[:N, :M].t()
+    got = kermac.cdist(a, b, out=out, p=1.0)
+    assert ko.rel_err_nonneg(got, ko.cdist_ref(a_h, b_h, p=1.0)[0]) < TOL_EXACT
+    assert float(big_out[N:].max()) == -7.0 and float(big_out[:, M:].max()) == -7.0
+
+
+# ------------------------------------------------------------------ batching / broadcasting / epilogue
+def test_batched_broadcast_fractional_p_with_and_without_epilogue():
+    # the shape family of the batched configuration: a[B, K, M] batched, b[1, K, N] broadcast
+    B, K, M, N = 4, 96, 300, 280
+    g = torch.Generator().manual_seed(2)
+    a_store = 2.0 * torch.rand(B, K, M, generator=g) - 1.0
+    b_store = 2.0 * torch.rand(1, K, N, generator=g) - 1.0
+    a, b = a_store.permute(0, 2, 1).cuda(), b_store.permute(0, 2, 1).cuda()
+    for b_arg in (b, b[0]):
+        full = kermac.cdist(a, b_arg, p=1.3)
+        raw = kermac.cdist(a, b_arg, p=1.3, skip_epilogue=True)
+        assert tuple(full.shape) == (B, M, N)
+        assert ko.rel_err_nonneg(full, ko.cdist_ref(a_store.permute(0, 2, 1), b_store.permute(0, 2, 1), p=1.3)) < TOL_FRAC
+        assert ko.rel_err_nonneg(raw, ko.cdist_ref(a_store.permute(0, 2, 1), b_store.permute(0, 2, 1), p=1.3,
+                                                   skip_epilogue=True)) < TOL_FRAC
+    # after skip_epilogue calls, a plain p=2 call still applies its square root
+    x = gen((50, 8), 3).cuda()
+    assert ko.rel_err_nonneg(kermac.cdist(x, x, p=2.0, skip_epilogue=True), ko.cdist_ref(x.cpu(), x.cpu(), 2.0, True)) < TOL_EXACT
+    assert ko.rel_err_nonneg(kermac.cdist(x, x, p=2.0), ko.cdist_ref(x.cpu(), x.cpu(), 2.0)) < TOL_EXACT
+
+
+def test_self_distance_diagonal_is_exactly_zero():
+    x = col_major(gen((300, 70), 5)).cuda()
+    for p in (1.0, 2.0, 1.3):
+        d = kermac.cdist(x, x, p=p)[0]
+        assert float(d.diagonal().abs().max()) == 0.0
+
+
+DESCRIPTOR_CASES = [
+    ("laplace_l1", dict(bandwidth=3.0), dict(inner_operator="DIFF", inner_power="ABS", outer_power="NOOP", kernel_type="LAPLACE")),
+    ("laplace_l2", dict(bandwidth=2.0), dict(inner_operator="DIFF", inner_power="SQUARE", outer_power="SQRT", kernel_type="LAPLACE")),
+    ("mma", dict(), dict(inner_operator="DOT", inner_power="NOOP", outer_power="NOOP", kernel_type="NONE")),
+]
+
+
+@pytest.mark.parametrize("name, kw, desc", DESCRIPTOR_CASES)
+def test_predefined_descriptors(name, kw, desc):
+    M, N, K = 210, 190, 24
+    a_h, b_h = gen((M, K), 51), gen((N, K), 52)
+    ref = ko.build_kernel_ref(a_h, b_h, **desc, **kw)[0]
+    for a in (a_h.cuda(), col_major(a_h).cuda()):
+        for out in (None, torch.empty(N, M, device="cuda").t()):
+            got = kermac.run_kernel(getattr(kermac, "kernel_descriptor_" + name), a, b_h.cuda(), out=out, **kw)
+            got = got[0] if got.dim() == 3 else got
+            if name == "mma":
+                assert ko.rel_err_signed(got, ref) < TOL_EXACT
+            else:
+                assert ko.rel_err_nonneg(got, ref) < TOL_FRAC
+
+
+CUSTOM = [
+    dict(inner_operator="DIFF", inner_power="SQUARE", outer_power="NOOP", kernel_type="GAUSSIAN"),
+    dict(inner_operator="DIFF", inner_power="NOOP", outer_power="ABS", kernel_type="NONE"),
+    dict(inner_operator="DIFF", inner_power="NOOP", outer_power="NOOP", kernel_type="NONE"),
+    dict(inner_operator="DIFF", inner_power="POW", outer_power="SQRT", kernel_type="NONE"),
+    dict(inner_operator="DOT", inner_power="SQUARE", outer_power="SQRT", kernel_type="NONE"),
+    dict(inner_operator="DOT", inner_power="ABS", outer_power="SQUARE", kernel_type="NONE"),
+    dict(inner_operator="DOT", inner_power="POW", outer_power="POW", kernel_type="NONE"),
+]
+
+
+@pytest.mark.parametrize("desc", CUSTOM)
+def test_custom_descriptors_both_output_layouts(desc):
+    M, N, K = 140, 133, 21
+    a_h, b_h = gen((M, K), 61, "rand"), gen((N, K), 62, "rand")
+    kw, okw = {}, {}
+    if desc["inner_power"] == "POW" and desc["outer_power"] == "POW":
+        kw["p"] = okw["p"] = 1.7
+    elif desc["inner_power"] == "POW":
+        kw["inner_p"] = okw["inner_p"] = 1.7
+    if desc["kernel_type"] != "NONE":
+        kw["bandwidth"] = okw["bandwidth"] = 1.5
+    kd = kermac.KernelDescriptor(getattr(kermac.InnerOperator, desc["inner_operator"]),
+                                 getattr(kermac.PowerType, desc["inner_power"]),
+                                 getattr(kermac.PowerType, desc["outer_power"]),
+                                 getattr(kermac.KernelType, desc["kernel_type"]))
+    ref = ko.build_kernel_ref(a_h, b_h, **desc, **okw)[0]
+    signed = desc["inner_power"] == "NOOP" and desc["outer_power"] == "NOOP"
+    for out in (torch.empty(M, N, device="cuda"), torch.empty(N, M, device="cuda").t()):
+        got = kermac.run_kernel(kd, a_h.cuda(), b_h.cuda(), out=out, **kw)
+        err = ko.rel_err_signed(got, ref) if signed else ko.rel_err_nonneg(got, ref)
+        assert err < TOL_FRAC, (desc, out.stride())
+
+
+def test_signed_sum_keeps_b_minus_a_for_row_major_out():
+    a_h, b_h = gen((40, 9), 63), gen((30, 9), 64)
+    kd = kermac.KernelDescriptor(kermac.InnerOperator.DIFF, kermac.PowerType.NOOP, kermac.PowerType.NOOP,
+                                 kermac.KernelType.NONE)
+    ref = (b_h.double().sum(1).unsqueeze(0) - a_h.double().sum(1).unsqueeze(1))
+    got = kermac.run_kernel(kd, a_h.cuda(), b_h.cuda(), out=torch.empty(40, 30, device="cuda"))
+    assert ko.rel_err_signed(got, ref) < TOL_EXACT
+
+
+def test_epsilon_mask_regularisation_and_offsets():
+    M, K = 150, 10
+    x_h = gen((M, K), 71)
+    x = x_h.cuda()
+    kw = dict(bandwidth=4.0, regularization=0.25, epsilon=1e-3)
+    desc = dict(inner_operator="DIFF", inner_power="SQUARE", outer_power="SQRT", kernel_type="LAPLACE")
+    for offs in ((0, 0), (3, 0), (0, 5)):
+        for out in (torch.empty(M, M, device="cuda"), torch.empty(M, M, device="cuda").t()):
+            got = kermac.run_kernel(kermac.kernel_descriptor_laplace_l2, x, x, out=out,
+                                    regularization_offset_x=offs[0], regularization_offset_y=offs[1], **kw)
+            ref = ko.build_kernel_ref(x_h, x_h, **desc, reg_off_x=offs[0], reg_off_y=offs[1], **kw)[0]
+            assert ko.rel_err_nonneg(got, ref) < TOL_FRAC
+            if offs == (0, 0):
+                assert torch.equal(got.diagonal().cpu(), torch.full((M,), 1.25))
+    # distances under epsilon give exactly 1 (masked to 0 before the exponential)
+    near = x_h.clone()
+    near[1] = near[0] + 1e-7
+    got = kermac.run_kernel(kermac.kernel_descriptor_laplace_l2, near.cuda(), near.cuda(), bandwidth=1.0)[0]
+    assert float(got[0, 1]) == 1.0 and float(got[1, 0]) == 1.0
+
+
+def test_batched_hyper_parameter_tensors():
+    L, M, N, K = 3, 90, 70, 12
+    a_h, b_h = gen((L, M, K), 81), gen((N, K), 82)
+    bw = torch.tensor([1.0, 2.5, 7.0])
+    reg = torch.tensor([0.0, 0.5, 0.0])
+    got = kermac.run_kernel(kermac.kernel_descriptor_laplace_l1, a_h.cuda(), b_h.cuda(), bandwidth=bw.cuda(),
+                            regularization=reg.cuda())
+    ref = ko.build_kernel_ref(a_h, b_h, "DIFF", "ABS", "NOOP", "LAPLACE", bandwidth=bw, regularization=reg)
+    assert ko.rel_err_nonneg(got, ref) < TOL_FRAC
+    p = torch.tensor([1.5, 2.0, 3.0])
+    got = kermac.run_kernel(kermac.kernel_descriptor_p_norm, a_h.cuda(), b_h.cuda(), p=p.cuda())
+    assert ko.rel_err_nonneg(got, ko.build_kernel_ref(a_h, b_h, "DIFF", "POW", "POW", "NONE", p=p)) < TOL_FRAC
+    scalar_bw = torch.tensor(2.0).cuda()          # 0-dim tensor broadcasts over the batch
+    got = kermac.run_kernel(kermac.kernel_descriptor_laplace_l2, a_h.cuda(), b_h.cuda(), bandwidth=scalar_bw)
+    assert ko.rel_err_nonneg(got, ko.build_kernel_ref(a_h, b_h, "DIFF", "SQUARE", "SQRT", "LAPLACE", bandwidth=2.0)) < TOL_FRAC
+
+
+def test_k_zero_and_empty_outputs():
+    a, b = torch.empty(5, 0, device="cuda"), torch.empty(4, 0, device="cuda")
+    assert float(kermac.cdist(a, b, p=2.0).abs().max()) == 0.0
+    assert tuple(kermac.cdist(torch.empty(0, 3, device="cuda"), torch.empty(4, 3, device="cuda")).shape) == (1, 0, 4)
+
+
+def test_runs_on_a_side_stream_without_synchronising():
+    a_h, b_h = gen((500, 64), 91), gen((400, 64), 92)
+    a, b = col_major(a_h).cuda(), col_major(b_h).cuda()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        got = kermac.cdist(a, b, p=1.0)
+    s.synchronize()
+    assert ko.rel_err_nonneg(got, ko.cdist_ref(a_h, b_h, p=1.0)) < TOL_EXACT
+
+
+# ------------------------------------------------------------------ full-size properties
+@pytest.mark.parametrize("p", [1.0, 2.0])
+def test_config2_full_size_sampled_rows_and_properties(p):
+    # a[K=1024, M=30000], b[K=1024, N=30000] ~ N(0,1) seed 1; 3.6 GB output on the device
+    K, M, N = 1024, 30000, 30000
+    g = torch.Generator().manual_seed(1)
+    a_store = torch.randn(K, M, generator=g)
+    b_store = torch.randn(K, N, generator=g)
+    a, b = a_store.cuda().t(), b_store.cuda().t()
+    out = torch.empty(N, M, device="cuda")
+    kermac.cdist(a, b, out=out.t(), p=p)
+    torch.cuda.synchronize()
+    # (1) oracle on sampled rows n, including tile-edge rows and the last row
+    rows = torch.tensor([0, 1, 127, 128, 129, 4095, 14999, 29951, 29952, 29999] +
+                        torch.randint(0, N, (22,), generator=g).tolist())
+    ref = ko.cdist_ref(a_store.t(), b_store.t()[rows], p=p)[0]          # (M, rows)
+    assert ko.rel_err_nonneg(out[rows.cuda()].t(), ref) < TOL_EXACT
+    # (2) size-independent properties: every entry finite and positive; swapping the operands
+    # transposes the result exactly (|b - a| == |a - b| term by term, same summation order)
+    assert bool(torch.isfinite(out).all()) and float(out.min()) > 0.0
+    sub = slice(12800, 13312)
+    swapped = kermac.cdist(b[sub], a[sub], p=p)[0]                      # (n, m) block
+    assert torch.equal(swapped, out[sub, sub])
+    # (3) a row-sharded call reproduces the same bits (what the multi-GPU path relies on)
+    part = torch.empty(3840, M, device="cuda")
+    kermac.cdist(a, b[3840:7680], out=part.t(), p=p)
+    assert torch.equal(part, out[3840:7680])

@@ -1,0 +1,81 @@
+"""Row sharding over ranks, exercised with world_size-2 (and 3) Gloo process groups on CPU.
+The compute step is the CPU oracle; what is under test is the partition and the gather."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from kermac_b200 import dist as kdist
+
+
+def test_slab_sizes_cover_and_align():
+    assert kdist.slab_sizes(10, 4) == [3, 3, 2, 2]
+    assert kdist.slab_sizes(30000, 8, 128) == [3840, 3840, 3840, 3712, 3712, 3712, 3712, 3632]
+    for n, w, al in [(0, 3, 128), (5, 8, 128), (1_000_000, 8, 128), (257, 2, 128), (128, 2, 128)]:
+        sizes = kdist.slab_sizes(n, w, al)
+        assert sum(sizes) == n and len(sizes) == w and all(s >= 0 for s in sizes)
+        starts = [sum(sizes[:r]) for r in range(w)]
+        assert all(st % al == 0 for st, s in zip(starts, sizes) if s > 0)
+    assert kdist.shard_rows(10, 2, 4) == (6, 8)
+    with pytest.raises(ValueError):
+        kdist.shard_rows(10, 4, 4)
+    with pytest.raises(ValueError):
+        kdist.slab_sizes(10, 0)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, n_total, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import kermac_oracle as ko
+        g = torch.Generator().manual_seed(0)
+        a = torch.randn(70, 9, generator=g)
+        b = torch.randn(n_total, 9, generator=g)
+        c = torch.randn(4, 70, generator=g)
+
+        def cdist_compute(a_, b_, out):
+            out.copy_(ko.cdist_ref(a_, b_, p=2.0)[0].float())
+
+        full = kdist.cdist_sharded(a, b, p=2.0, compute=cdist_compute)
+        slab = kdist.cdist_sharded(a, b, p=2.0, compute=cdist_compute, gather=False)
+        ref = ko.cdist_ref(a, b, p=2.0)[0].float().t().contiguous()       # [n][m]
+        start, stop = kdist.shard_rows(n_total, rank, world, kdist.ROW_ALIGN)
+        ok = torch.equal(full, ref) and torch.equal(slab, ref[start:stop])
+
+        def mv_compute(a_, b_, c_, out):
+            out.copy_(ko.kernel_matvec_ref(a_, b_, c_, inner_operator="DIFF", inner_power="SQUARE",
+                                           outer_power="SQRT", kernel_type="LAPLACE", bandwidth=8.0)[0].float())
+
+        y = kdist.kernel_matvec_sharded(None, a, b, c, compute=mv_compute)
+        yref = ko.kernel_matvec_ref(a, b, c, inner_operator="DIFF", inner_power="SQUARE", outer_power="SQRT",
+                                    kernel_type="LAPLACE", bandwidth=8.0)[0].float()
+        ok = ok and torch.equal(y, yref)
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world, n_total", [(2, 256), (2, 300), (3, 130), (2, 100)])
+def test_sharded_ops_on_gloo_ranks(world, n_total):
+    # 256 rows -> equal slabs (single all_gather_into_tensor); 300 / 130 -> unequal slabs (padded
+    # gather); 100 rows on 2 ranks -> the second rank owns nothing
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n_total, results)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert all(results.get(r) for r in range(world)), dict(results)
