@@ -229,7 +229,8 @@ def test_custom_descriptors_both_output_layouts(desc):
                                  getattr(kermac.PowerType, desc["outer_power"]),
                                  getattr(kermac.KernelType, desc["kernel_type"]))
     ref = ko.build_kernel_ref(a_h, b_h, **desc, **okw)[0]
-    signed = desc["inner_power"] == "NOOP" and desc["outer_power"] == "NOOP"
+    # a sum of signed differences cancels, so it is judged against the largest entry
+    signed = desc["inner_power"] == "NOOP"
     for out in (torch.empty(M, N, device="cuda"), torch.empty(N, M, device="cuda").t()):
         got = kermac.run_kernel(kd, a_h.cuda(), b_h.cuda(), out=out, **kw)
         err = ko.rel_err_signed(got, ref) if signed else ko.rel_err_nonneg(got, ref)
