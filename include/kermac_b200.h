@@ -142,6 +142,27 @@ int kermac_b200_cdist_grad(const KmGradArgs* args, void* stream);
 int64_t kermac_b200_cdist_grad_scratch_bytes(const KmGradArgs* args);
 
 /*
+ * Same computation and arguments as kermac_b200_cdist_grad, for callers that cannot
+ * allocate device memory where they call it (a plugin inside another runtime's fixed
+ * memory pool, a latency-bound loop that must not enter an allocator, a foreign-function
+ * layer that can only forward the pointers it was given).  The partial sums of the k
+ * split go to an array that is part of the library image, KM_GRAD_STATIC_SCRATCH_BYTES
+ * large, which every GPU that loads the library holds until the process exits.
+ * args->scratch and args->scratch_bytes are ignored.  The call never allocates.
+ *   - A problem whose k split (args->split_k, or the automatic choice when 0) needs more
+ *     than KM_GRAD_STATIC_SCRATCH_BYTES is rejected with KM_ERR_TOO_LARGE; split_k = 1
+ *     always fits (single pass, no scratch).
+ *   - All calls share the one array and it keeps the previous call's contents.  Nothing
+ *     in it needs clearing (each call writes every partial it later reads), but calls that
+ *     overlap on the GPU race on it: order them on one stream or with events.
+ *   - The first call on each device looks up the array's device address with the CUDA
+ *     runtime; make that first call outside any stream capture.
+ * It has no counterpart in the reference.
+ */
+#define KM_GRAD_STATIC_SCRATCH_BYTES (64LL << 20)
+int kermac_b200_cdist_grad_static(const KmGradArgs* args, void* stream);
+
+/*
  * y[l, n, o] = sum_m Kfn( outer( sum_k inner( b[l, n, k] (-|*) a[l, m, k] ) ) ) * c[l, o, m]
  * with the same inner / outer / kernel-function chain (epsilon mask included) as
  * kermac_b200_build_kernel, but the (m, n) kernel matrix is never stored.

@@ -24,6 +24,7 @@ EXPORTED_SYMBOLS = (
     "kermac_b200_build_kernel",
     "kermac_b200_cdist_grad",
     "kermac_b200_cdist_grad_scratch_bytes",
+    "kermac_b200_cdist_grad_static",
     "kermac_b200_kernel_matvec",
     "kermac_b200_kernel_matvec_scratch_bytes",
     "kermac_b200_describe_variant",
@@ -107,6 +108,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.kermac_b200_cdist_grad.restype = C.c_int
     lib.kermac_b200_cdist_grad_scratch_bytes.argtypes = [C.POINTER(KmGradArgs)]
     lib.kermac_b200_cdist_grad_scratch_bytes.restype = C.c_int64
+    lib.kermac_b200_cdist_grad_static.argtypes = [C.POINTER(KmGradArgs), C.c_void_p]
+    lib.kermac_b200_cdist_grad_static.restype = C.c_int
     lib.kermac_b200_kernel_matvec.argtypes = [C.POINTER(KmMatvecArgs), C.c_void_p]
     lib.kermac_b200_kernel_matvec.restype = C.c_int
     lib.kermac_b200_kernel_matvec_scratch_bytes.argtypes = [C.POINTER(KmMatvecArgs)]
@@ -190,6 +193,15 @@ def launch_build(args: KmBuildArgs, stream_ptr: int) -> None:
 
 def launch_grad(args: KmGradArgs, stream_ptr: int) -> None:
     check(lib().kermac_b200_cdist_grad(C.byref(args), C.c_void_p(stream_ptr)), "kermac_b200_cdist_grad")
+
+
+GRAD_STATIC_SCRATCH_BYTES = 64 << 20
+
+
+def launch_grad_static(args: KmGradArgs, stream_ptr: int) -> None:
+    """cdist_grad whose k-split scratch is the library's built-in array: for callers that
+    must not allocate.  Shares one array between all calls; see include/kermac_b200.h."""
+    check(lib().kermac_b200_cdist_grad_static(C.byref(args), C.c_void_p(stream_ptr)), "kermac_b200_cdist_grad_static")
 
 
 def launch_matvec(args: KmMatvecArgs, stream_ptr: int) -> None:

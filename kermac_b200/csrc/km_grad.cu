@@ -10,6 +10,8 @@
 //   - the contracted k range can be split over several thread blocks, whose partial
 //     tiles go to caller-provided scratch and are summed in a fixed order by a
 //     second kernel, so results do not depend on scheduling.
+#include <mutex>
+
 #include "km_common.cuh"
 #include "km_host.h"
 
@@ -370,4 +372,81 @@ extern "C" int kermac_b200_cdist_grad(const KmGradArgs* args, void* stream) {
         if (int rc = cuda_status(cudaGetLastError(), "launch of grad_reduce_kernel")) return rc;
     }
     return 0;
+}
+
+// ---------------------------------------------------------------------------
+// kermac_b200_cdist_grad_static: the split-k gradient for callers that have no way
+// to hand over scratch memory.
+//
+// Some hosts of this library may not allocate device memory at the point where they
+// call it: a plugin running inside another runtime's memory pool with a fixed budget,
+// a real-time loop whose latency budget excludes allocator calls, or a binding whose
+// foreign-function layer only passes through the pointers it was given.  For them the
+// partial sums of the k split live in the array below, which is part of the library
+// image: every GPU that loads the library carries it (KM_GRAD_STATIC_SCRATCH_BYTES)
+// from load until the process exits.
+//
+// Rules that follow from sharing one array:
+//   * it keeps whatever the previous call left in it.  Nothing in it has to start at
+//     zero, because every partial tile a call reads back is first written in full by
+//     that same call;
+//   * two calls whose kernels overlap on the GPU (different streams, different host
+//     threads) would write the same partials and corrupt each other: callers must
+//     order them;
+//   * the first call on each device looks up the array's device address.  That lookup
+//     is a runtime API call, so make the first call per device outside any stream
+//     capture.
+namespace km {
+namespace {
+
+constexpr long long KM_GRAD_STATIC_FLOATS = KM_GRAD_STATIC_SCRATCH_BYTES / 4;
+static __device__ __align__(256) float g_grad_static_scratch[KM_GRAD_STATIC_FLOATS];
+
+// Device address of g_grad_static_scratch per device ordinal.  In host code the
+// array's name only stands for the symbol; the address a kernel can use has to be
+// asked for with the owning device current.
+float*     g_grad_static_ptr[64] = {nullptr};
+std::mutex g_grad_static_mutex;
+
+int grad_static_scratch(float** out) {
+    int dev = -1;
+    if (int rc = cuda_status(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    if (dev < 0 || dev >= 64) return fail(KM_ERR_INTERNAL, "device ordinal %d is out of range", dev);
+    std::lock_guard<std::mutex> lock(g_grad_static_mutex);
+    if (!g_grad_static_ptr[dev]) {
+        void* p = nullptr;
+        if (int rc = cuda_status(cudaGetSymbolAddress(&p, g_grad_static_scratch),
+                                 "cudaGetSymbolAddress(g_grad_static_scratch)"))
+            return rc;
+        if (!p) return fail(KM_ERR_INTERNAL, "the static scratch array has no device address");
+        g_grad_static_ptr[dev] = static_cast<float*>(p);
+    }
+    *out = g_grad_static_ptr[dev];
+    return 0;
+}
+
+}  // namespace
+}  // namespace km
+
+extern "C" int kermac_b200_cdist_grad_static(const KmGradArgs* args, void* stream) {
+    using namespace km;
+    if (!args) return fail(KM_ERR_NULL_POINTER, "args is NULL");
+    KmGradArgs local   = *args;
+    local.scratch      = nullptr;
+    local.scratch_bytes = 0;
+    // How much scratch the requested (or automatic) k split needs; 0 means a single pass.
+    const int64_t need = kermac_b200_cdist_grad_scratch_bytes(&local);
+    const int64_t cap  = KM_GRAD_STATIC_FLOATS * 4;
+    if (need > cap)
+        return fail(KM_ERR_TOO_LARGE,
+                    "this problem's k split needs %lld bytes of scratch but the built-in array holds %lld; "
+                    "pass split_k = 1, or call kermac_b200_cdist_grad with your own scratch",
+                    (long long)need, (long long)cap);
+    if (need > 0) {
+        float* ptr = nullptr;
+        if (int rc = grad_static_scratch(&ptr)) return rc;
+        local.scratch       = ptr;
+        local.scratch_bytes = cap;
+    }
+    return kermac_b200_cdist_grad(&local, stream);
 }
