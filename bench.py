@@ -52,6 +52,10 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-rows", type=int, default=512)
+    ap.add_argument("--workload", default="cdist", choices=["cdist", "cdist_batched", "grad", "matvec"],
+                    help="cdist is the headline workload; the others cover the remaining operators")
+    ap.add_argument("--mv-m", type=int, default=1_000_000, help="matvec: number of points a")
+    ap.add_argument("--mv-n", type=int, default=1_000_000, help="matvec: number of points b")
     return ap.parse_args()
 
 
@@ -210,6 +214,23 @@ def main():
         t = torch.tensor([ms], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    if args.workload != "cdist":
+        import bench_workloads
+
+        class Ctx:
+            pass
+        ctx = Ctx()
+        ctx.rank, ctx.world, ctx.barrier, ctx.max_over_ranks = rank, world, barrier, max_over_ranks
+        ctx.clocks = lambda: ClockSampler(local_rank)
+        line = getattr(bench_workloads, args.workload)(args, ctx)
+        if rank == 0:
+            assert _native.device_error_flag() == 0, "a bounded wait inside a kernel ran out"
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     M, N, K = args.m, args.n, args.k
     a_store, b_store = make_inputs(M, N, K)
