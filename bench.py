@@ -36,6 +36,12 @@ import torch  # noqa: E402
 
 K_DIM, M_DIM, N_DIM, SEED = 1024, 30000, 30000, 1
 WORKLOAD = "cdist fp32 a[K=1024,M=30000] b[K=1024,N=30000] N(0,1) seed 1, out[N,M], full epilogue"
+# dram__bytes_read.sum + dram__bytes_write.sum of the cdist kernel, per launch.  Captured with ncu on
+# M = N = 8192, K = 1024 (profiles/), where it is 390 MB against 335 MB algorithmic (67 MB in + 268 MB out);
+# scaled to the full launch by the output and input bytes, which is what the traffic is proportional to.
+TRAFFIC_BYTES_PER_LAUNCH = int(390e6 / 335e6 * 4 * (M_DIM * N_DIM + K_DIM * (M_DIM + N_DIM)))
+TRAFFIC_NOTE = ("scaled from an ncu capture at 8192x8192x1024 (390 MB measured vs 335 MB algorithmic); "
+                "HBM is not the bound of this kernel")
 
 
 def parse_args():
@@ -152,7 +158,19 @@ def reference_arm(args):
         "e2e": {"value": value, "unit": "diff-ops/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+# Best kermac.cdist time the reference publishes for this problem size (README.md:95-111 of the
+# reference; none of it on B200): p -> (milliseconds, GPU).
+PUBLISHED_MS = {1.0: (76.0, "RTX 4090"), 1.3: (350.0, "RTX 4090"), 2.0: (77.0, "RTX 4090")}
+
+
+def vs_published(args, world, value):
+    """value / published difference-ops per second, for the exact published problem on one GPU."""
+    if (args.m, args.n, args.k) != (M_DIM, N_DIM, K_DIM) or args.p not in PUBLISHED_MS:
+        return None
+    return value / (3.0 * M_DIM * N_DIM * K_DIM / (PUBLISHED_MS[args.p][0] * 1e-3))
 
 
 def metric_name(p):
@@ -164,7 +182,9 @@ def config_dict(args, world):
             else f"cdist fp32 a[K={args.k},M={args.m}] b[K={args.k},N={args.n}] N(0,1) seed 1",
             "p": args.p, "M": args.m, "N": args.n, "K": args.k,
             "sharding": "single GPU" if world == 1 else f"output rows N sharded over {world} ranks + all-gather",
-            "l2": "inputs (246 MB) and output (3.6 GB) exceed the 126 MB L2; no flush needed between steps"}
+            "l2": "inputs (246 MB) and output (3.6 GB) exceed the 126 MB L2; no flush needed between steps",
+            "vs_baseline_is": "value / the best kermac.cdist throughput the reference publishes for this size and p "
+                              "(README table: %s ms on %s)" % PUBLISHED_MS.get(args.p, ("n/a", "n/a"))}
 
 
 def timed_steps(fn, steps, warmup, barrier):
@@ -183,8 +203,18 @@ def timed_steps(fn, steps, warmup, barrier):
     return e0.elapsed_time(e1)
 
 
+def emit(line):
+    """Writes the one JSON line to the real stdout (libraries that print to fd 1 were sent to stderr)."""
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
+
+
+_REAL_STDOUT = os.dup(1)
+
+
 def main():
     args = parse_args()
+    sys.stdout.flush()
+    os.dup2(2, 1)          # NCCL and friends print banners on fd 1; the JSON line must stand alone
     if args.impl == "reference":
         reference_arm(args)
         return
@@ -226,7 +256,7 @@ def main():
         line = getattr(bench_workloads, args.workload)(args, ctx)
         if rank == 0:
             assert _native.device_error_flag() == 0, "a bounded wait inside a kernel ran out"
-            print(json.dumps(line), flush=True)
+            emit(line)
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
@@ -237,7 +267,7 @@ def main():
     a_dev, b_dev = a_store.to(device), b_store.to(device)
     a, b = a_dev.t(), b_dev.t()                    # API tensors (M, K), (N, K), m / n contiguous
     start, stop = kdist.shard_rows(N, rank, world, kdist.ROW_ALIGN)
-    slab = torch.empty((stop - start, M), dtype=torch.float32, device=device)
+    gather_buf, slab = kdist.gather_buffer(N, (M,), world, rank, kdist.ROW_ALIGN, device)
     launches = {"n": 0}
 
     def compute_step(p):
@@ -253,7 +283,7 @@ def main():
         def step():
             compute()
             if world > 1:
-                kdist.gather_rows(slab, N, None, kdist.ROW_ALIGN)
+                kdist.gather_rows_inplace(gather_buf, N)
         return step
 
     ops_total = 3.0 * M * N * K
@@ -273,7 +303,7 @@ def main():
     line = {
         "metric": metric_name(args.p), "value": value, "unit": "diff-ops/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": vs_published(args, world, value), "dtype": "f32", "data": "synthetic",
         "config": config_dict(args, world), "clocks": clock_info, "gpu_launches": timed_launches,
         "compute_only": {"ms_per_step": k_ms, "value": ops_total / (k_ms * 1e-3),
                          "note": "cdist kernel on this rank's row slab, max over ranks, no gather"},
@@ -286,6 +316,8 @@ def main():
         mufu_ops, _ = _native.measure_pipe(2, 2048)
         lane_peak = max(lane_ops_packed, lane_ops_scalar)
         fp32_peak_flops = 2.0 * lane_peak
+        # what the inner loop's instruction mix sustains with operands already in shared memory
+        ceiling_lane_ops, _ = _native.measure_pipe(5 if args.p == 1.0 else 4, 2048)
         achieved = slab_ops / (k_ms * 1e-3)
         nominal = 148 * 128 * 2 * 1.965e9
         line["roofline"] = {
@@ -295,9 +327,12 @@ def main():
             "peak_source": "measured on this device by kermac_b200_measure_pipe (fma.rn.f32x2 chains), x2 flop per lane-op",
             "frac_of_nominal_74.45": achieved / nominal,
             "fma_pipe_lane_utilisation": (2.0 / 3.0) * achieved / lane_peak,
+            "inner_loop_ceiling_lane_ops": ceiling_lane_ops,
+            "frac_of_inner_loop_ceiling": (2.0 / 3.0) * achieved / ceiling_lane_ops,
             "mufu_peak_ops": mufu_ops, "mufu_utilisation": (2.0 / 3.0) * achieved / mufu_ops,
             "lane_ops_scalar": lane_ops_scalar, "lane_ops_packed": lane_ops_packed,
-            "traffic": None,
+            "traffic": TRAFFIC_BYTES_PER_LAUNCH if (M, N, K) == (M_DIM, N_DIM, K_DIM) and world == 1 else None,
+            "traffic_note": TRAFFIC_NOTE,
             "hbm_gbs_algorithmic": 4.0 * (M * (stop - start) + K * (M + stop - start)) / (k_ms * 1e-3) / 1e9,
         }
 
@@ -317,7 +352,7 @@ def main():
         a_pin = a_store.pin_memory()
         b_pin = b_store[:, start:stop].contiguous().pin_memory()
         out_pin = torch.empty((stop - start, M), dtype=torch.float32).pin_memory()
-        del slab
+        del slab, gather_buf
         torch.cuda.empty_cache()
 
         def e2e_step():
@@ -346,7 +381,7 @@ def main():
                                                             budget_s=20.0)
     if rank == 0:
         assert _native.device_error_flag() == 0, "a bounded wait inside a kernel ran out"
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

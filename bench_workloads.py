@@ -182,7 +182,7 @@ def matvec(args, ctx):
     c = torch.randn(O, M, generator=g)
     ad, bd, cd = a_store.cuda().t(), b_store.cuda().t(), c.cuda()
     start, stop = kdist.shard_rows(N, ctx.rank, ctx.world, kdist.ROW_ALIGN)
-    slab = torch.empty(stop - start, O, device="cuda")
+    gather_buf, slab = kdist.gather_buffer(N, (O,), ctx.world, ctx.rank, kdist.ROW_ALIGN, torch.device("cuda"))
     launches = {"n": 0}
 
     def compute():
@@ -193,7 +193,7 @@ def matvec(args, ctx):
     def job():
         compute()
         if ctx.world > 1:
-            kdist.gather_rows(slab, N, None, kdist.ROW_ALIGN)
+            kdist.gather_rows_inplace(gather_buf, N)
 
     with ctx.clocks() as clocks:
         ms = ctx.max_over_ranks(_timed(job, args.steps, args.warmup, ctx.barrier))

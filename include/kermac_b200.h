@@ -196,6 +196,9 @@ int kermac_b200_describe_variant(const KmBuildArgs* args, char* buf, int32_t buf
  *   kind 1: packed fma.rn.f32x2      -> result in FP32 lane-operations per second
  *   kind 2: MUFU (lg2.approx + ex2.approx) -> result in MUFU operations per second
  *   kind 3: scalar add.f32 (sub then add-abs chain, the p=1 inner step)
+ *   kind 4: the cdist p=2 inner loop (shared-memory operand loads, duplicate moves, packed
+ *           sub + fma) with no global staging -> FP32 lane-operations per second
+ *   kind 5: the same for the p=1 inner loop (packed sub + add|.|)
  * Synchronises the device.  Returns 0 and stores the rate in *ops_per_second.
  */
 int kermac_b200_measure_pipe(int32_t kind, int32_t iterations, double* ops_per_second, double* milliseconds);

@@ -75,6 +75,52 @@ __device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) {
     return r;
 }
 
+// ---------------------------------------------------------------- exp2 on the FP32 pipe
+// The fractional-power inner step costs two MUFU operations per element (lg2, ex2)
+// and the MUFU pipe has 16 lanes per SM against 128 FP32 lanes, so a kernel that
+// sends both through MUFU is MUFU-bound with the FP32 pipe three quarters idle.
+// ex2_poly2 evaluates 2^x for a packed pair on the FP32 pipe instead, so a share of
+// the elements needs only one MUFU operation.
+//
+//   t     = x + (1.5 * 2^23 + 127)      round x to the nearest integer n; the low bits
+//                                       of t then hold n + 127, the biased exponent
+//   f     = x - (t - magic)             in [-0.5, 0.5]
+//   r     = 2^f                         degree-5 polynomial, max relative error 2.9e-7
+//                                       (ex2.approx is specified to 2 ulp = 2.4e-7)
+//   scale = bits(t) << 23               2^n as a float
+// The caller folds the scaling into its accumulate: acc = fma2(r, scale, acc).
+// x is clamped to [-127, 128] first: at -127 (which is where lg2(0) * p = -inf lands)
+// scale is exactly +0 and r exactly 1, so a zero difference still adds exactly 0; at
+// 128 scale is +inf.  The clamps use the NaN-propagating min / max, so a NaN input
+// still produces NaN (NaN * scale).
+__device__ __forceinline__ float max_nan(float a, float b) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ float min_nan(float a, float b) {
+    float r;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void ex2_poly2(float x0, float x1, u64& r, u64& scale) {
+    x0 = min_nan(max_nan(x0, -127.0f), 128.0f);
+    x1 = min_nan(max_nan(x1, -127.0f), 128.0f);
+    const u64 x     = pack2(x0, x1);
+    const u64 magic = pack2(12583039.0f, 12583039.0f);
+    const u64 t     = add2(x, magic);
+    const u64 f     = sub2(x, sub2(t, magic));
+    // 2^f = 1 + f (c1 + f (c2 + f (c3 + f (c4 + f c5))))
+    u64 q = fma2(f, pack2(1.3390867e-3f, 1.3390867e-3f), pack2(9.6663740e-3f, 9.6663740e-3f));
+    q     = fma2(q, f, pack2(5.5503570e-2f, 5.5503570e-2f));
+    q     = fma2(q, f, pack2(2.4022348e-1f, 2.4022348e-1f));
+    q     = fma2(q, f, pack2(6.9314718e-1f, 6.9314718e-1f));
+    r     = fma2(q, f, pack2(1.0f, 1.0f));
+    float t0, t1;
+    unpack2(t, t0, t1);
+    scale = pack2(__int_as_float(__float_as_int(t0) << 23), __int_as_float(__float_as_int(t1) << 23));
+}
+
 // ---------------------------------------------------------------- async copies
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -207,6 +253,17 @@ __device__ __forceinline__ void inner_block(u64 (&acc)[8][4], const u64 (&ap)[4]
                     a0 += fabsf(d0);
                     a1 += fabsf(d1);
                 } else if constexpr (INNER == IN_DIFF_POW || INNER == IN_DOT_POW) {
+                    if (mp != 3) {
+                        // three of every four pairs: lg2 on MUFU, the exponential on the FP32
+                        // pipe; this balances the two pipes (see ex2_poly2)
+                        const u64 x = mul2(pack2(lg2_approx(fabsf(d0)), lg2_approx(fabsf(d1))), pack2(p_inner, p_inner));
+                        float x0, x1;
+                        unpack2(x, x0, x1);
+                        u64 r, scale;
+                        ex2_poly2(x0, x1, r, scale);
+                        acc[n][mp] = fma2(r, scale, acc[n][mp]);
+                        continue;
+                    }
                     a0 += pow_approx(fabsf(d0), p_inner);
                     a1 += pow_approx(fabsf(d1), p_inner);
                 } else if constexpr (INNER == IN_DIFF_NOOP) {
@@ -244,8 +301,11 @@ __device__ __forceinline__ void consume_slab(u64 (&acc)[8][4], const float* sa, 
         const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
         inner_block<INNER>(acc, ap, bv, p_inner, sgn);
     };
+    // The fractional-power step is ~30 instructions per element; unrolling all BK rows of
+    // it would not fit the instruction cache, so it is unrolled by 2 only.
+    constexpr int UNROLL = (INNER == IN_DIFF_POW || INNER == IN_DOT_POW) ? 2 : BK;
     if (kvalid >= BK) {
-#pragma unroll
+#pragma unroll UNROLL
         for (int kk = 0; kk < BK; ++kk) step(kk);
     } else {
 #pragma unroll 1

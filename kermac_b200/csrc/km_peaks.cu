@@ -2,7 +2,7 @@
 // bound by.  They give the roofline denominators (fp32 lane-operations per second,
 // MUFU operations per second) for the device and clock the benchmark actually
 // runs at, instead of a nominal figure.
-#include "km_common.cuh"
+#include "km_build_params.cuh"
 #include "km_host.h"
 
 namespace km {
@@ -52,6 +52,45 @@ __global__ void __launch_bounds__(PEAK_THREADS) pipe_kernel(float* sink, int ite
     if (s == 123.456f) sink[0] = s;   // keeps the chains alive without a store in practice
 }
 
+// The product inner loop (consume_slab: 128-bit shared loads, duplicate moves, packed
+// sub / fma or sub / add|.|) running from a shared-memory slab that is filled once, with
+// no global staging, barriers or epilogue: the ceiling the instruction mix itself allows.
+template <int INNER>
+__global__ void __launch_bounds__(256, 2) inner_loop_kernel(float* sink, int slabs, float seed) {
+    constexpr int BK = BUILD_CPA_BK, PITCH = BUILD_CPA_PITCH;
+    __shared__ __align__(16) float sa[BK * PITCH];
+    __shared__ __align__(16) float sb[BK * PITCH];
+    for (int i = threadIdx.x; i < BK * PITCH; i += 256) {
+        sa[i] = seed + 1e-3f * i;
+        sb[i] = seed - 2e-3f * i;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* pa = sa + (warp & 1) * 64 + (lane & 7) * 4;
+    const float* pb = sb + (warp >> 1) * 32 + (lane >> 3) * 4;
+    u64 acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0ull;
+    for (int s = 0; s < slabs; ++s) {
+        // alternate the start row (0 or 4; rows shift .. shift + 11 stay inside the 16-row
+        // slab) so the loads are not loop invariant
+        const int shift = (s & 1) * 4;
+        consume_slab<INNER, BK - 4, PITCH>(acc, pa + shift * PITCH, pb + shift * PITCH, BK, 1.3f, 1.0f);
+    }
+    float t = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float lo, hi;
+            unpack2(acc[j][i], lo, hi);
+            t += lo + hi;
+        }
+    if (t == 123.456f) sink[0] = t;
+}
+
 typedef void (*PipeFn)(float*, int, float);
 
 }  // namespace
@@ -61,13 +100,14 @@ extern "C" int kermac_b200_measure_pipe(int32_t kind, int32_t iterations, double
                                         double* milliseconds) {
     using namespace km;
     if (!ops_per_second) return fail(KM_ERR_NULL_POINTER, "ops_per_second is NULL");
-    if (kind < 0 || kind > 3) return fail(KM_ERR_BAD_ENUM, "kind %d is not a pipe benchmark", kind);
+    if (kind < 0 || kind > 5) return fail(KM_ERR_BAD_ENUM, "kind %d is not a pipe benchmark", kind);
     if (iterations < 1 || iterations > (1 << 24)) return fail(KM_ERR_BAD_SHAPE, "iterations out of range");
     if (int rc = require_sm100()) return rc;
-    PipeFn fns[4] = {pipe_kernel<0>, pipe_kernel<1>, pipe_kernel<2>, pipe_kernel<3>};
+    PipeFn fns[6] = {pipe_kernel<0>, pipe_kernel<1>, pipe_kernel<2>, pipe_kernel<3>,
+                     inner_loop_kernel<IN_DIFF_SQUARE>, inner_loop_kernel<IN_DIFF_ABS>};
     float* sink   = nullptr;
     if (int rc = cuda_status(cudaMalloc(&sink, 256), "cudaMalloc")) return rc;
-    const int blocks = sm_count() * 8;
+    const int blocks = sm_count() * (kind >= 4 ? 2 : 8);
     cudaEvent_t e0, e1;
     cudaEventCreate(&e0);
     cudaEventCreate(&e1);
@@ -84,7 +124,9 @@ extern "C" int kermac_b200_measure_pipe(int32_t kind, int32_t iterations, double
     if (rc) return rc;
     // lane-operations per inner statement: fma = 1 (x2 when packed), MUFU pair = 2, sub+add = 2
     const double per_stmt = (kind == 1) ? 2.0 : (kind == 0 ? 1.0 : 2.0);
-    const double total    = per_stmt * 8.0 * PEAK_CHAINS * (double)iterations * (double)blocks * PEAK_THREADS;
+    double total          = per_stmt * 8.0 * PEAK_CHAINS * (double)iterations * (double)blocks * PEAK_THREADS;
+    // inner-loop kinds: `iterations` slabs of 12 k rows, 64 element-steps per thread and row, 2 lane-ops each
+    if (kind >= 4) total = 2.0 * 64.0 * (BUILD_CPA_BK - 4) * (double)iterations * (double)blocks * PEAK_THREADS;
     *ops_per_second       = total / (ms * 1e-3);
     if (milliseconds) *milliseconds = ms;
     return 0;

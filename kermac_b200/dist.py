@@ -16,15 +16,17 @@ from typing import Callable, Optional, Tuple
 import torch
 import torch.distributed as dist_
 
-__all__ = ["shard_rows", "slab_sizes", "gather_rows", "cdist_sharded", "kernel_matvec_sharded"]
+__all__ = ["shard_rows", "slab_sizes", "gather_buffer", "gather_rows_inplace", "gather_rows", "cdist_sharded",
+           "kernel_matvec_sharded"]
 
 
 ROW_ALIGN = 128   # slab boundaries fall on output-tile boundaries (and keep slices 16-byte aligned)
 
 
 def slab_sizes(n: int, world: int, align: int = 1) -> list:
-    """Rows per rank: whole units of `align` rows, as equal as possible, earlier ranks
-    take the remainder; the last non-empty slab is cut so the sizes sum to n."""
+    """Rows per rank: every rank gets the same slab of whole `align`-row units, except that
+    the last non-empty slab is cut where the rows end (trailing ranks may own nothing).
+    Equal slabs make the all-gather a single in-place collective whose result needs no copy."""
     if world < 1:
         raise ValueError("world must be >= 1")
     if n < 0:
@@ -32,8 +34,8 @@ def slab_sizes(n: int, world: int, align: int = 1) -> list:
     if align < 1:
         raise ValueError("align must be >= 1")
     units = -(-n // align)
-    base, extra = divmod(units, world)
-    bounds = [min(n, align * (r * base + min(r, extra))) for r in range(world + 1)]
+    slab = align * (-(-units // world))
+    bounds = [min(n, r * slab) for r in range(world + 1)]
     return [bounds[r + 1] - bounds[r] for r in range(world)]
 
 
@@ -46,12 +48,33 @@ def shard_rows(n: int, rank: int, world: int, align: int = 1) -> Tuple[int, int]
     return start, start + sizes[rank]
 
 
+def gather_buffer(n_total: int, tail: tuple, world: int, rank: int, align: int, device, dtype=torch.float32):
+    """(buffer, slab): a (world * slab_rows, *tail) buffer and the view of it that rank `rank`
+    fills.  After `gather_rows_inplace` the first n_total rows of the buffer are the result."""
+    sizes = slab_sizes(n_total, world, align)
+    largest = max(sizes) if sizes else 0
+    buf = torch.empty((world * largest,) + tuple(tail), dtype=dtype, device=device)
+    return buf, buf[rank * largest: rank * largest + sizes[rank]]
+
+
+def gather_rows_inplace(buf: torch.Tensor, n_total: int, group=None) -> torch.Tensor:
+    """In-place all-gather of the equal-size slabs of `buf` (see gather_buffer); returns the
+    contiguous view buf[:n_total].  Rows of a short or empty last slab carry padding that is
+    exchanged but never read."""
+    world = dist_.get_world_size(group)
+    if world > 1:
+        rank = dist_.get_rank(group)
+        largest = buf.size(0) // world
+        dist_.all_gather_into_tensor(buf, buf[rank * largest: (rank + 1) * largest], group=group)
+    return buf[:n_total]
+
+
 def gather_rows(local: torch.Tensor, n_total: int, group=None, align: int = 1) -> torch.Tensor:
     """All-gathers row slabs (dim 0) of shape (rows_r, ...) into (n_total, ...).
 
-    `local` must be contiguous; slabs must follow `slab_sizes(n_total, world, align)`.  Equal
-    slabs use one `all_gather_into_tensor`; unequal ones are padded to the largest slab
-    for the collective and trimmed afterwards.
+    `local` must be contiguous and follow `slab_sizes(n_total, world, align)`.  This form
+    copies the local slab into the gather buffer; operators that can write their slab in
+    place use `gather_buffer` + `gather_rows_inplace` instead.
     """
     world = dist_.get_world_size(group)
     rank = dist_.get_rank(group)
@@ -60,20 +83,11 @@ def gather_rows(local: torch.Tensor, n_total: int, group=None, align: int = 1) -
         raise ValueError(f"rank {rank} holds {local.size(0)} rows, expected {sizes[rank]}")
     if not local.is_contiguous():
         raise ValueError("local slab must be contiguous")
-    tail = tuple(local.shape[1:])
     if world == 1:
         return local
-    largest = max(sizes)
-    if all(s == largest for s in sizes):
-        full = torch.empty((n_total,) + tail, dtype=local.dtype, device=local.device)
-        dist_.all_gather_into_tensor(full, local, group=group)
-        return full
-    padded = torch.zeros((largest,) + tail, dtype=local.dtype, device=local.device)
-    padded[: sizes[rank]] = local
-    buf = torch.empty((world * largest,) + tail, dtype=local.dtype, device=local.device)
-    dist_.all_gather_into_tensor(buf, padded, group=group)
-    pieces = [buf[r * largest: r * largest + sizes[r]] for r in range(world)]
-    return torch.cat(pieces, dim=0)
+    buf, slab = gather_buffer(n_total, tuple(local.shape[1:]), world, rank, align, local.device, local.dtype)
+    slab.copy_(local)
+    return gather_rows_inplace(buf, n_total, group)
 
 
 def cdist_sharded(a: torch.Tensor, b: torch.Tensor, p: float = 2.0, skip_epilogue: bool = False,
@@ -90,7 +104,10 @@ def cdist_sharded(a: torch.Tensor, b: torch.Tensor, p: float = 2.0, skip_epilogu
     rank = dist_.get_rank(group) if dist_.is_initialized() else 0
     n_total, m_total = b.size(0), a.size(0)
     start, stop = shard_rows(n_total, rank, world, ROW_ALIGN)
-    slab = torch.empty((stop - start, m_total), dtype=torch.float32, device=a.device)
+    if gather and world > 1:
+        buf, slab = gather_buffer(n_total, (m_total,), world, rank, ROW_ALIGN, a.device)
+    else:
+        buf, slab = None, torch.empty((stop - start, m_total), dtype=torch.float32, device=a.device)
     if compute is None:
         from .cdist import cdist as _cdist
 
@@ -99,9 +116,9 @@ def cdist_sharded(a: torch.Tensor, b: torch.Tensor, p: float = 2.0, skip_epilogu
     if stop > start:
         # `slab` is [n][m] storage; the operator's out is (M, rows) with m contiguous.
         compute(a, b[start:stop], slab.t())
-    if not gather or world == 1:
+    if buf is None:
         return slab
-    return gather_rows(slab, n_total, group, ROW_ALIGN)
+    return gather_rows_inplace(buf, n_total, group)
 
 
 def kernel_matvec_sharded(kernel_descriptor, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
@@ -114,7 +131,10 @@ def kernel_matvec_sharded(kernel_descriptor, a: torch.Tensor, b: torch.Tensor, c
     rank = dist_.get_rank(group) if dist_.is_initialized() else 0
     n_total = b.size(0)
     start, stop = shard_rows(n_total, rank, world, ROW_ALIGN)
-    slab = torch.empty((stop - start, c.size(0)), dtype=torch.float32, device=a.device)
+    if gather and world > 1:
+        buf, slab = gather_buffer(n_total, (c.size(0),), world, rank, ROW_ALIGN, a.device)
+    else:
+        buf, slab = None, torch.empty((stop - start, c.size(0)), dtype=torch.float32, device=a.device)
     if compute is None:
         from .matvec import kernel_matvec as _matvec
 
@@ -122,6 +142,6 @@ def kernel_matvec_sharded(kernel_descriptor, a: torch.Tensor, b: torch.Tensor, c
             return _matvec(kernel_descriptor, a_, b_, c_, out=out, **hyper)
     if stop > start:
         compute(a, b[start:stop], c, slab)
-    if not gather or world == 1:
+    if buf is None:
         return slab
-    return gather_rows(slab, n_total, group, ROW_ALIGN)
+    return gather_rows_inplace(buf, n_total, group)

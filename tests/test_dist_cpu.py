@@ -12,14 +12,14 @@ from kermac_b200 import dist as kdist
 
 
 def test_slab_sizes_cover_and_align():
-    assert kdist.slab_sizes(10, 4) == [3, 3, 2, 2]
-    assert kdist.slab_sizes(30000, 8, 128) == [3840, 3840, 3840, 3712, 3712, 3712, 3712, 3632]
+    assert kdist.slab_sizes(10, 4) == [3, 3, 3, 1]
+    assert kdist.slab_sizes(30000, 8, 128) == [3840] * 7 + [3120]
     for n, w, al in [(0, 3, 128), (5, 8, 128), (1_000_000, 8, 128), (257, 2, 128), (128, 2, 128)]:
         sizes = kdist.slab_sizes(n, w, al)
         assert sum(sizes) == n and len(sizes) == w and all(s >= 0 for s in sizes)
         starts = [sum(sizes[:r]) for r in range(w)]
         assert all(st % al == 0 for st, s in zip(starts, sizes) if s > 0)
-    assert kdist.shard_rows(10, 2, 4) == (6, 8)
+    assert kdist.shard_rows(10, 2, 4) == (6, 9)
     with pytest.raises(ValueError):
         kdist.shard_rows(10, 4, 4)
     with pytest.raises(ValueError):
