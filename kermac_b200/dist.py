@@ -17,7 +17,7 @@ import torch
 import torch.distributed as dist_
 
 __all__ = ["shard_rows", "slab_sizes", "gather_buffer", "gather_rows_inplace", "gather_rows", "cdist_sharded",
-           "kernel_matvec_sharded"]
+           "OverlappedCdist", "kernel_matvec_sharded"]
 
 
 ROW_ALIGN = 128   # slab boundaries fall on output-tile boundaries (and keep slices 16-byte aligned)
@@ -119,6 +119,112 @@ def cdist_sharded(a: torch.Tensor, b: torch.Tensor, p: float = 2.0, skip_epilogu
     if buf is None:
         return slab
     return gather_rows_inplace(buf, n_total, group)
+
+
+class OverlappedCdist:
+    """Row-sharded `cdist` that moves the result to the other ranks while it is computed.
+
+    Rank r owns the contiguous slab of rows `shard_rows(N, r, world, 128)` of the result
+    [n][m].  The slab is computed in `chunks` launches; as soon as a launch is done, its
+    rows are pushed into the same rows of every peer's result buffer by peer-to-peer
+    copies, which the copy engines carry over NVLink without occupying an SM, while the
+    next launch computes.  Only the last chunk's push and one cross-rank barrier are not
+    hidden.  (A collective on the SMs cannot overlap here: the distance kernels fill every
+    SM's register file, so a communication kernel only gets to run between launches.)
+
+    The result buffer is symmetric memory (`torch.distributed._symmetric_memory`), allocated
+    and exchanged once per object and reused by every `run`.  With `transport="collective"`,
+    or when the tensors are not on CUDA, the slabs are exchanged by one in-place all-gather
+    after the last launch instead.
+    """
+
+    def __init__(self, M: int, N: int, device, group=None, chunks: int = 8, transport: str = "auto"):
+        if transport not in ("auto", "peer_copy", "collective"):
+            raise ValueError("transport must be 'auto', 'peer_copy' or 'collective'")
+        device = torch.device(device)
+        self.group = group
+        self.world = dist_.get_world_size(group) if dist_.is_initialized() else 1
+        self.rank = dist_.get_rank(group) if dist_.is_initialized() else 0
+        self.M, self.N = M, N
+        self.sizes = slab_sizes(N, self.world, ROW_ALIGN)
+        self.slab_rows = max(self.sizes) if self.sizes else 0
+        self.start = sum(self.sizes[:self.rank])
+        self.rows = self.sizes[self.rank]
+        self.chunks = max(1, chunks)
+        if transport == "auto":
+            transport = "peer_copy" if (device.type == "cuda" and self.world > 1) else "collective"
+        self.transport = transport
+        shape = (self.world * self.slab_rows, M)
+        self._handle, self._peers, self._streams, self._second = None, None, None, None
+        if transport == "peer_copy":
+            import torch.distributed._symmetric_memory as symm_mem
+            self.full = symm_mem.empty(shape, dtype=torch.float32, device=device)
+            self._handle = symm_mem.rendezvous(self.full, group=dist_.group.WORLD if group is None else group)
+            self._peers = [self._handle.get_buffer(r, shape, torch.float32) for r in range(self.world)]
+            self._streams = [torch.cuda.Stream(device=device) for _ in range(self.world)]
+        else:
+            self.full = torch.empty(shape, dtype=torch.float32, device=device)
+
+    def chunk_bounds(self):
+        """[(row0, row1)] of the launches inside this rank's slab, on 128-row boundaries."""
+        per = ROW_ALIGN * max(1, -(-(-(-self.rows // ROW_ALIGN)) // self.chunks))
+        return [(r0, min(self.rows, r0 + per)) for r0 in range(0, self.rows, per)]
+
+    def run(self, a: torch.Tensor, b: torch.Tensor, p: float = 2.0, skip_epilogue: bool = False,
+            gather: bool = True, compute: Optional[Callable] = None) -> torch.Tensor:
+        """a (M, K) and b (N, K) identical on every rank.  Returns the (N, M) result [n][m],
+        complete on every rank when `gather`; otherwise only this rank's rows are valid.
+        The returned tensor aliases the object's buffer: the next `run` overwrites it."""
+        if a.dim() != 2 or b.dim() != 2 or a.size(0) != self.M or b.size(0) != self.N:
+            raise ValueError("operands do not match the shapes this object was built for")
+        if compute is None:
+            from .cdist import cdist as _cdist
+
+            def compute(a_, b_, out):
+                return _cdist(a_, b_, out=out, p=p, skip_epilogue=skip_epilogue)
+        push = gather and self.world > 1 and self.transport == "peer_copy"
+        on_cuda = self.full.is_cuda
+        main = torch.cuda.current_stream() if on_cuda else None
+        if push:
+            self._handle.barrier()          # nobody is still reading the buffer a peer is about to fill
+        bounds = self.chunk_bounds()
+        # Launches alternate between the caller's stream and a second one: they write disjoint
+        # rows, so the next launch's thread blocks fill the SMs the previous one's last wave
+        # leaves idle instead of waiting for it to drain.
+        second = None
+        if on_cuda and len(bounds) > 1:
+            if self._second is None:
+                self._second = torch.cuda.Stream(device=self.full.device)
+            second = self._second
+            second.wait_stream(main)
+        for g, (r0, r1) in enumerate(bounds):
+            rows = slice(self.start + r0, self.start + r1)
+            stream = second if (second is not None and g % 2 == 1) else main
+            if stream is main:
+                compute(a, b[rows], self.full[rows].t())
+            else:
+                with torch.cuda.stream(stream):
+                    compute(a, b[rows], self.full[rows].t())
+            if push:
+                done = torch.cuda.Event()
+                done.record(stream)
+                for r in range(self.world):
+                    if r == self.rank:
+                        continue
+                    copier = self._streams[r]
+                    copier.wait_event(done)
+                    with torch.cuda.stream(copier):
+                        self._peers[r][rows].copy_(self.full[rows], non_blocking=True)
+        if second is not None:
+            main.wait_stream(second)
+        if push:
+            for r in range(self.world):
+                if r != self.rank:
+                    main.wait_stream(self._streams[r])
+            self._handle.barrier()          # every rank's pushes into this buffer have landed
+        elif gather and self.world > 1:
+            gather_rows_inplace(self.full, self.N, self.group)
+        return self.full[:self.N]
 
 
 def kernel_matvec_sharded(kernel_descriptor, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,

@@ -52,6 +52,14 @@ def _worker(rank, world, port, n_total, results):
         start, stop = kdist.shard_rows(n_total, rank, world, kdist.ROW_ALIGN)
         ok = torch.equal(full, ref) and torch.equal(slab, ref[start:stop])
 
+        # chunked slab variant; on CPU ranks it takes the collective transport
+        for chunks in (1, 3):
+            ov = kdist.OverlappedCdist(70, n_total, "cpu", chunks=chunks)
+            ok = ok and ov.transport == "collective"
+            ok = ok and torch.equal(ov.run(a, b, p=2.0, compute=cdist_compute), ref)
+            covered = sum(r1 - r0 for r0, r1 in ov.chunk_bounds())
+            ok = ok and covered == stop - start
+
         def mv_compute(a_, b_, c_, out):
             out.copy_(ko.kernel_matvec_ref(a_, b_, c_, inner_operator="DIFF", inner_power="SQUARE",
                                            outer_power="SQRT", kernel_type="LAPLACE", bandwidth=8.0)[0].float())
@@ -65,7 +73,7 @@ def _worker(rank, world, port, n_total, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world, n_total", [(2, 256), (2, 300), (3, 130), (2, 100)])
+@pytest.mark.parametrize("world, n_total", [(2, 256), (2, 300), (3, 130), (2, 100), (2, 1000)])
 def test_sharded_ops_on_gloo_ranks(world, n_total):
     # 256 rows -> equal slabs (single all_gather_into_tensor); 300 / 130 -> unequal slabs (padded
     # gather); 100 rows on 2 ranks -> the second rank owns nothing

@@ -36,6 +36,13 @@ def _worker(rank, world, port, results):
             single = torch.empty(1000, 700, device="cuda")
             kermac.cdist(a, b, out=single.t(), p=p)
             ok = ok and torch.equal(full, single)                 # sharding must not change a single bit
+        for transport in ("peer_copy", "collective"):
+            ov = kdist.OverlappedCdist(700, 1000, torch.device("cuda", rank), chunks=3, transport=transport)
+            for p in (1.0, 2.0, 1.3):
+                single = torch.empty(1000, 700, device="cuda")
+                kermac.cdist(a, b, out=single.t(), p=p)
+                ok = ok and torch.equal(ov.run(a, b, p=p), single)
+                ok = ok and torch.equal(ov.run(a, b, p=p), single)     # the buffer is reused run after run
         y = kdist.kernel_matvec_sharded(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=8.0)
         y1 = kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=8.0)[0]
         ok = ok and torch.equal(y, y1)
