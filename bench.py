@@ -362,7 +362,7 @@ def main():
         line["also"] = also
 
     if not args.no_e2e:
-        pipe = HostCdist(M, stop - start, K, device=device, slabs=8)
+        pipe = HostCdist(M, stop - start, K, device=device, slabs=16)
         a_pin = a_store.pin_memory()
         b_pin = b_store[:, start:stop].contiguous().pin_memory()
         out_pin = torch.empty((stop - start, M), dtype=torch.float32).pin_memory()

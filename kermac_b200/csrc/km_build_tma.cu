@@ -222,25 +222,45 @@ bool operand_tma_ok(const float* base, long long s_t, long long s_k, long long s
 
 typedef void (*TmaKernelFn)(const BuildParams, const CUtensorMap, const CUtensorMap);
 
-constexpr int kBK     = 16;
-constexpr int kStages = 6;
-constexpr int kLag    = 2;
-constexpr int kSmemBytes = kStages * 2 * kBK * TMA_TILE * 4 + 128;
+// Pipeline shape per inner step: k rows per TMA box / stage, ring depth, and how many
+// slabs thread 0's refill of a stage trails its own consumption.  Measured on B200 at
+// 30000 x 30000 x 1024: for the square and product steps 32-row slabs (3 stages) run 2 %
+// faster than 16-row slabs (6 stages), 54.6 vs 55.8 ms, because fewer slab boundaries
+// interrupt the load scheduling; the |.| and |.|^p steps are slower with deep slabs.
+template <int INNER>
+struct TmaShape {
+    static constexpr bool deep = (INNER == IN_DIFF_SQUARE || INNER == IN_DOT_NOOP);
+    static constexpr int BK     = deep ? 32 : 16;
+    static constexpr int STAGES = deep ? 3 : 6;
+    static constexpr int LAG    = deep ? 1 : 2;
+    static constexpr int SMEM   = STAGES * 2 * BK * TMA_TILE * 4 + 128;
+};
 
-TmaKernelFn tma_kernel(int inner) {
+struct TmaChoice {
+    TmaKernelFn fn;
+    int bk, smem;
+};
+
+template <int INNER>
+TmaChoice tma_choice() {
+    typedef TmaShape<INNER> S;
+    return {build_tma_kernel<INNER, S::BK, S::STAGES, S::LAG>, S::BK, S::SMEM};
+}
+
+TmaChoice tma_kernel(int inner) {
     switch (inner) {
-        case IN_DIFF_ABS: return build_tma_kernel<IN_DIFF_ABS, kBK, kStages, kLag>;
-        case IN_DIFF_SQUARE: return build_tma_kernel<IN_DIFF_SQUARE, kBK, kStages, kLag>;
-        case IN_DIFF_POW: return build_tma_kernel<IN_DIFF_POW, kBK, kStages, kLag>;
-        case IN_DOT_NOOP: return build_tma_kernel<IN_DOT_NOOP, kBK, kStages, kLag>;
+        case IN_DIFF_ABS: return tma_choice<IN_DIFF_ABS>();
+        case IN_DIFF_SQUARE: return tma_choice<IN_DIFF_SQUARE>();
+        case IN_DIFF_POW: return tma_choice<IN_DIFF_POW>();
+        case IN_DOT_NOOP: return tma_choice<IN_DOT_NOOP>();
     }
-    return nullptr;
+    return {nullptr, 0, 0};
 }
 
 }  // namespace
 
 bool tma_supported(const BuildParams& p) {
-    if (!tma_kernel(p.inner_id)) return false;
+    if (!tma_kernel(p.inner_id).fn) return false;
     if (p.K < 1) return false;
     return operand_tma_ok(p.A, p.a_sm, p.a_sk, p.a_sl, p.K, p.L) && operand_tma_ok(p.B, p.b_sn, p.b_sk, p.b_sl, p.K, p.L);
 }
@@ -249,12 +269,14 @@ bool tma_supported(const BuildParams& p) {
 // product steps (55.9 vs 57.0 ms); for |.| and |.|^p the cp.async kernel is ahead
 // (61.4 vs 64.2 ms, 403 vs 431 ms), so those keep it.
 bool tma_preferred(const BuildParams& p) {
-    return p.K >= 2 * kBK && (p.inner_id == IN_DIFF_SQUARE || p.inner_id == IN_DOT_NOOP);
+    return p.K >= 64 && (p.inner_id == IN_DIFF_SQUARE || p.inner_id == IN_DOT_NOOP);
 }
 
 int launch_build_tma(const BuildParams& p, cudaStream_t stream) {
-    TmaKernelFn fn = tma_kernel(p.inner_id);
+    const TmaChoice choice = tma_kernel(p.inner_id);
+    TmaKernelFn fn         = choice.fn;
     if (!fn) return fail(KM_ERR_INTERNAL, "no TMA kernel for inner id %d", p.inner_id);
+    const int kBK = choice.bk, kSmemBytes = choice.smem;
     if (int rc = cuda_status(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
                              "cudaFuncSetAttribute(build_tma_kernel)"))
         return rc;

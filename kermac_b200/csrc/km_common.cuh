@@ -253,9 +253,11 @@ __device__ __forceinline__ void inner_block(u64 (&acc)[8][4], const u64 (&ap)[4]
                     a0 += fabsf(d0);
                     a1 += fabsf(d1);
                 } else if constexpr (INNER == IN_DIFF_POW || INNER == IN_DOT_POW) {
-                    if (mp != 3) {
-                        // three of every four pairs: lg2 on MUFU, the exponential on the FP32
-                        // pipe; this balances the two pipes (see ex2_poly2)
+                    if (mp != 3 && !(mp == 1 && (n & 1))) {
+                        // five of every eight pairs: lg2 on MUFU, the exponential on the FP32
+                        // pipe.  A pair costs ~30 issue slots this way against ~10 (and 32 MUFU
+                        // cycles instead of 16) the all-MUFU way; 5/8 is where the instruction
+                        // issue rate and the MUFU pipe are loaded about equally.
                         const u64 x = mul2(pack2(lg2_approx(fabsf(d0)), lg2_approx(fabsf(d1))), pack2(p_inner, p_inner));
                         float x0, x1;
                         unpack2(x, x0, x1);
@@ -301,8 +303,9 @@ __device__ __forceinline__ void consume_slab(u64 (&acc)[8][4], const float* sa, 
         const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
         inner_block<INNER>(acc, ap, bv, p_inner, sgn);
     };
-    // The fractional-power step is ~30 instructions per element; unrolling all BK rows of
-    // it would not fit the instruction cache, so it is unrolled by 2 only.
+    // The whole slab is unrolled, so operand loads are scheduled ahead of the math across all
+    // of its rows.  The fractional-power step is ~30 instructions per element; unrolling it
+    // that far would not fit the instruction cache, so it is unrolled by 2 only.
     constexpr int UNROLL = (INNER == IN_DIFF_POW || INNER == IN_DOT_POW) ? 2 : BK;
     if (kvalid >= BK) {
 #pragma unroll UNROLL

@@ -134,15 +134,31 @@ __global__ void __launch_bounds__(G_THREADS, 2) grad_kernel(const __grid_constan
     auto step = [&](const float* sa, const float* sb, const float* sc, int kk) {
         const ulonglong2 a4 = *reinterpret_cast<const ulonglong2*>(sa + kk * PITCH_A + tmi * 4);
         const u64 av[2]     = {a4.x, a4.y};
+        // b and c rows of this k: 128-bit shared loads where the tile shape allows
         float bv[NT];
+        if constexpr (NT == 4) {
+            const float4 b4 = *reinterpret_cast<const float4*>(sb + kk * PITCH_B + tni * 4);
+            bv[0] = b4.x; bv[1] = b4.y; bv[2] = b4.z; bv[3] = b4.w;
+        } else if constexpr (NT == 2) {
+            const float2 b2 = *reinterpret_cast<const float2*>(sb + kk * PITCH_B + tni * 2);
+            bv[0] = b2.x; bv[1] = b2.y;
+        } else {
+            bv[0] = sb[kk * PITCH_B + tni];
+        }
+        float cv[OT];
+        if constexpr (OT >= 4) {
 #pragma unroll
-        for (int j = 0; j < NT; ++j) bv[j] = sb[kk * PITCH_B + tni * NT + j];
+            for (int o = 0; o < OT; o += 4) {
+                const float4 c4 = *reinterpret_cast<const float4*>(sc + kk * PITCH_C + o);
+                cv[o] = c4.x; cv[o + 1] = c4.y; cv[o + 2] = c4.z; cv[o + 3] = c4.w;
+            }
+        } else {
+#pragma unroll
+            for (int o = 0; o < OT; ++o) cv[o] = sc[kk * PITCH_C + o];
+        }
         u64 cd[OT];
 #pragma unroll
-        for (int o = 0; o < OT; ++o) {
-            const float cv = sc[kk * PITCH_C + o];
-            cd[o]          = pack2(cv, cv);
-        }
+        for (int o = 0; o < OT; ++o) cd[o] = pack2(cv[o], cv[o]);
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
             const u64 bd = pack2(bv[j], bv[j]);
@@ -157,9 +173,21 @@ __global__ void __launch_bounds__(G_THREADS, 2) grad_kernel(const __grid_constan
                 } else {
                     float d0, d1;
                     unpack2(diff, d0, d1);
-                    const float g0 = copysignf(pow_approx(fabsf(d0), pm1), d0);
-                    const float g1 = copysignf(pow_approx(fabsf(d1), pm1), d1);
-                    w              = mul2(av[h], pack2(g0, g1));
+                    if (h == 0 && (j & 1) == 0 && NT > 1) {
+                        // one pair in four takes only lg2 on MUFU and the exponential on the
+                        // FP32 pipe (ex2_poly2); more than that and instruction issue, not MUFU,
+                        // becomes the limit
+                        const u64 x = mul2(pack2(lg2_approx(fabsf(d0)), lg2_approx(fabsf(d1))), pack2(pm1, pm1));
+                        float x0, x1;
+                        unpack2(x, x0, x1);
+                        u64 r, scale;
+                        ex2_poly2(x0, x1, r, scale);
+                        w = mul2(av[h], flip_sign2(mul2(r, scale), diff));
+                    } else {
+                        const float g0 = copysignf(pow_approx(fabsf(d0), pm1), d0);
+                        const float g1 = copysignf(pow_approx(fabsf(d1), pm1), d1);
+                        w              = mul2(av[h], pack2(g0, g1));
+                    }
                 }
 #pragma unroll
                 for (int o = 0; o < OT; ++o) acc[j][o][h] = fma2(cd[o], w, acc[j][o][h]);
