@@ -225,6 +225,15 @@ __host__ __device__ inline int inner_id(int op, int power) {
     return -1;
 }
 
+// Which of the 8 x 4 element pairs of a register block take their exponential on the FP32
+// pipe (ex2_poly2) rather than on MUFU: KM_POW_POLY_EIGHTHS of every 8 pairs.
+#ifndef KM_POW_POLY_EIGHTHS
+#define KM_POW_POLY_EIGHTHS 6
+#endif
+__device__ __forceinline__ constexpr bool pow_pair_uses_fp32_exp(int n, int mp) {
+    return ((n & 1) * 4 + mp) < KM_POW_POLY_EIGHTHS;
+}
+
 // One k step of an 8 (rows of the pair-packed operand) x 8 register block.
 //   ap[4]  : the 8 values of the m-side operand as 4 packed pairs (m, m+1)
 //   bv[8]  : the 8 values of the n-side operand
@@ -253,11 +262,10 @@ __device__ __forceinline__ void inner_block(u64 (&acc)[8][4], const u64 (&ap)[4]
                     a0 += fabsf(d0);
                     a1 += fabsf(d1);
                 } else if constexpr (INNER == IN_DIFF_POW || INNER == IN_DOT_POW) {
-                    if (mp != 3 && !(mp == 1 && (n & 1))) {
-                        // five of every eight pairs: lg2 on MUFU, the exponential on the FP32
-                        // pipe.  A pair costs ~30 issue slots this way against ~10 (and 32 MUFU
-                        // cycles instead of 16) the all-MUFU way; 5/8 is where the instruction
-                        // issue rate and the MUFU pipe are loaded about equally.
+                    if (pow_pair_uses_fp32_exp(n, mp)) {
+                        // most pairs: lg2 on MUFU, the exponential on the FP32 pipe.  A pair costs
+                        // ~30 issue slots this way against ~10 (and 32 MUFU cycles instead of 16)
+                        // the all-MUFU way; the share is set where the kernel measured fastest.
                         const u64 x = mul2(pack2(lg2_approx(fabsf(d0)), lg2_approx(fabsf(d1))), pack2(p_inner, p_inner));
                         float x0, x1;
                         unpack2(x, x0, x1);
