@@ -17,13 +17,29 @@ from cuda.bindings import nvrtc
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 
-BUILD = "cute_build_kernel<InnerOperator::DIFF,PowerType::{inner},PowerType::{outer},KernelType::NONE," \
-        "Majorness::COL_MAJOR,Majorness::COL_MAJOR,Alignment::{al},Alignment::{al}>"
+BUILD = "cute_build_kernel<InnerOperator::{op},PowerType::{inner},PowerType::{outer},KernelType::{kernel}," \
+        "Majorness::{ma},Majorness::{mb},Alignment::{al},Alignment::{al}>"
+
+
+def build(inner, outer, kernel="NONE", op="DIFF", ma="COL_MAJOR", mb="COL_MAJOR", al="ALIGN_4"):
+    return BUILD.format(op=op, inner=inner, outer=outer, kernel=kernel, ma=ma, mb=mb, al=al)
+
+
 NAMES = {}
 for al in ("ALIGN_1", "ALIGN_4"):
-    NAMES[f"cdist_p1_{al}"] = BUILD.format(inner="ABS", outer="NOOP", al=al)
-    NAMES[f"cdist_p2_{al}"] = BUILD.format(inner="SQUARE", outer="SQRT", al=al)
-    NAMES[f"cdist_pow_{al}"] = BUILD.format(inner="POW", outer="POW", al=al)
+    NAMES[f"cdist_p1_{al}"] = build("ABS", "NOOP", al=al)
+    NAMES[f"cdist_p2_{al}"] = build("SQUARE", "SQRT", al=al)
+    NAMES[f"cdist_pow_{al}"] = build("POW", "POW", al=al)
+# the other descriptors and the skipped epilogues (column-major operands, 16-byte copies)
+NAMES["l2_raw"] = build("SQUARE", "NOOP")
+NAMES["pow_raw"] = build("POW", "NOOP")
+NAMES["laplace_l1"] = build("ABS", "NOOP", "LAPLACE")
+NAMES["laplace_l2"] = build("SQUARE", "SQRT", "LAPLACE")
+NAMES["gaussian_l2sq"] = build("SQUARE", "NOOP", "GAUSSIAN")
+NAMES["mma"] = build("NOOP", "NOOP", op="DOT")
+# row-major operands (4-byte copies only in the reference)
+NAMES["cdist_p2_rowmajor"] = build("SQUARE", "SQRT", ma="ROW_MAJOR", mb="ROW_MAJOR", al="ALIGN_1")
+NAMES["cdist_p1_row_col"] = build("ABS", "NOOP", ma="ROW_MAJOR", mb="COL_MAJOR", al="ALIGN_1")
 NAMES["grad_L1"] = "cute_norm_kernel_gradient<NormType::L1>"
 NAMES["grad_L2"] = "cute_norm_kernel_gradient<NormType::L2>"
 NAMES["grad_P"] = "cute_norm_kernel_gradient<NormType::P>"

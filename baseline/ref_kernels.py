@@ -48,7 +48,8 @@ def _function(key: str):
         with open(CUBIN, "rb") as f:
             _state["module"] = _check(drv.cuModuleLoadData(f.read()))
         with open(NAMES) as f:
-            _state["names"] = json.load(f)["lowered"]
+            names = json.load(f)
+        _state["names"], _state["expressions"] = names["lowered"], names["expressions"]
     if key not in _state:
         drv = _driver()
         _state[key] = _check(drv.cuModuleGetFunction(_state["module"], _state["names"][key].encode()))
@@ -75,6 +76,10 @@ def ref_cdist(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, p: float, ali
     al = "ALIGN_4" if aligned else "ALIGN_1"
     key = {1.0: "cdist_p1_", 2.0: "cdist_p2_"}.get(p, "cdist_pow_") + al
     fn = _function(key)
+    if aligned:
+        for t, ld, what in ((a3, lda, "a"), (b3, ldb, "b")):
+            if t.data_ptr() % 16 != 0 or ld % 4 != 0 or (t.size(0) > 1 and t.stride(0) % 4 != 0):
+                raise ValueError(f"{what} is not 16-byte aligned (pointer, pitch or batch stride)")
     dev = a.device
     p_inner = torch.tensor(float(p) if key.startswith("cdist_pow") else 0.0, dtype=torch.float32, device=dev)
     p_outer = 1.0 / p_inner if key.startswith("cdist_pow") else torch.tensor(0.0, dtype=torch.float32, device=dev)
@@ -89,6 +94,52 @@ def ref_cdist(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, p: float, ali
     stream = torch.cuda.current_stream().cuda_stream
     _check(_driver().cuLaunchKernel(fn, grid[0], grid[1], grid[2], 256, 1, 1, 0, _driver().CUstream(stream), (values, types), 0))
     _state["keep"] = (p_inner, p_outer, zero)
+    return out
+
+
+def _ld(t: torch.Tensor, row_major: bool, what: str):
+    if t.dim() == 2:
+        t = t.unsqueeze(0)
+    if row_major:
+        if t.stride(-1) != 1:
+            raise ValueError(f"{what} must have its second matrix index contiguous")
+        ld = t.stride(-2)
+    else:
+        if t.stride(-2) != 1:
+            raise ValueError(f"{what} must have its first matrix index contiguous")
+        ld = t.stride(-1)
+    return t, ld, (0 if t.size(0) == 1 else t.stride(0))
+
+
+def ref_run_kernel(key: str, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, p_inner: float = 0.0,
+                   p_outer: float = 0.0, bandwidth: float = 0.0, regularization: float = 0.0, off_x: int = 0,
+                   off_y: int = 0, epsilon: float = 1e-5, a_row_major: bool = False, b_row_major: bool = False):
+    """Launches the `cute_build_kernel` instantiation built under `key` (see build_ref_cubin.py) with scalar
+    hyper-parameters.  `out` must have its first matrix index contiguous (the kernel writes column-major C)."""
+    a3, lda, bsa = _ld(a, a_row_major, "a")
+    b3, ldb, bsb = _ld(b, b_row_major, "b")
+    c3, ldc, bsc = _ld(out, False, "out")
+    L = max(a3.size(0), b3.size(0))
+    M, K = a3.shape[-2:]
+    N = b3.shape[-2]
+    fn = _function(key)
+    if "ALIGN_4" in _state["expressions"][key]:
+        # the 16-byte-copy instantiations fault on anything else (the reference's host code only
+        # selects them after the same check, src/kermac/common.py:110-116)
+        for t, ld, what in ((a3, lda, "a"), (b3, ldb, "b")):
+            if t.data_ptr() % 16 != 0 or ld % 4 != 0 or (t.size(0) > 1 and t.stride(0) % 4 != 0):
+                raise ValueError(f"{what} is not 16-byte aligned (pointer, pitch or batch stride) for {key}")
+    hyper = torch.tensor([p_inner, p_outer, bandwidth, regularization], dtype=torch.float32, device=a.device)
+    hp = hyper.data_ptr()
+    values = (M, N, K, L,
+              a3.data_ptr(), lda, bsa, b3.data_ptr(), ldb, bsb, c3.data_ptr(), ldc, bsc,
+              hp, 0, hp + 4, 0, hp + 8, 0, hp + 12, 0, off_x, off_y, epsilon)
+    types = (C.c_int32,) * 4 + (C.c_void_p, C.c_uint64, C.c_uint64) * 3 + (C.c_void_p, C.c_uint64) * 4 + \
+            (C.c_int32, C.c_int32, C.c_float)
+    grid = ((M + 127) // 128, (N + 127) // 128, L)
+    stream = torch.cuda.current_stream().cuda_stream
+    _check(_driver().cuLaunchKernel(fn, grid[0], grid[1], grid[2], 256, 1, 1, 0, _driver().CUstream(stream), (values, types), 0))
+    _state["keep_hyper"] = hyper
     return out
 
 

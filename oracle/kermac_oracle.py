@@ -26,7 +26,9 @@ time (tests/test_cdist.py:75, tests/test_cdist_grad.py:43-49).  This oracle is p
 against exactly those two torch formulations in float64 (tests/test_oracle.py and the
 fixtures under tests/golden/).  The operator variants the reference never tests
 (skip_epilogue, gradient p != 2, Laplace / Gaussian / epsilon / regularisation, DOT)
-are pinned only by this restatement of the kernel source: parity unpinned for those.
+have no pin on the CPU side beyond this restatement of the kernel source; on a GPU box they are
+additionally compared with the reference's own kernels (tests/test_vs_reference_kernels_gpu.py).
+Still parity unpinned: batched hyper-parameter tensors and the fused kernel_matvec.
 """
 from __future__ import annotations
 
