@@ -2,7 +2,7 @@
 // accepts (either majorness, any pitch, any base alignment).
 //
 // A thread block of 256 threads owns one 128 (m) x 128 (n) output tile and walks
-// k in slabs of 16 through a 3-stage cp.async pipeline.  Both operands are staged
+// k in slabs of 32 through a 3-stage cp.async pipeline.  Both operands are staged
 // k-major with the tile dimension contiguous ([k][128 + pad]) whatever their
 // layout in global memory, so the math loop reads them with 128-bit shared loads:
 //   - an operand whose tile dimension is contiguous and 16-byte aligned is copied
@@ -28,17 +28,17 @@ constexpr int CPA_THREADS = BUILD_CPA_THREADS;
 constexpr int CPA_STAGE_FLOATS = 2 * CPA_BK * CPA_PITCH;
 constexpr int CPA_SMEM_BYTES   = BUILD_CPA_SMEM_BYTES;
 
-// Stages the k slab `kt` of one operand tile into `dst` ([CPA_BK][CPA_PITCH]).
+// Stages the k slab `kt` (BK rows) of one operand tile into `dst` ([BK][CPA_PITCH]).
 //   base  : first element of the tile (row 0 of the tile dimension, k = 0)
 //   s_t   : stride of the tile dimension, s_k: stride of k
 //   rem_t : valid extent of the tile dimension (may exceed 128)
-template <bool VEC>
+template <bool VEC, int BK = CPA_BK>
 __device__ __forceinline__ void stage_operand(float* dst, const float* base, long long s_t, long long s_k, int rem_t,
                                               int K, int kt, int tid) {
-    const int k0 = kt * CPA_BK;
+    const int k0 = kt * BK;
     if constexpr (VEC) {
 #pragma unroll
-        for (int i = 0; i < (CPA_BK * CPA_TILE / 4) / CPA_THREADS; ++i) {
+        for (int i = 0; i < (BK * CPA_TILE / 4) / CPA_THREADS; ++i) {
             const int idx = tid + i * CPA_THREADS;
             const int kk  = idx >> 5;
             const int t   = (idx & 31) << 2;
@@ -51,12 +51,12 @@ __device__ __forceinline__ void stage_operand(float* dst, const float* base, lon
     } else {
         const bool k_contig = (s_k == 1);
 #pragma unroll
-        for (int i = 0; i < (CPA_BK * CPA_TILE) / CPA_THREADS; ++i) {
+        for (int i = 0; i < (BK * CPA_TILE) / CPA_THREADS; ++i) {
             const int idx = tid + i * CPA_THREADS;
             int kk, t;
             if (k_contig) {
-                kk = idx & (CPA_BK - 1);
-                t  = idx >> 4;
+                kk = idx & (BK - 1);
+                t  = idx / BK;
             } else {
                 t  = idx & (CPA_TILE - 1);
                 kk = idx >> 7;

@@ -11,7 +11,10 @@ namespace km {
 // Geometry shared by the launcher and the build kernels.
 constexpr int BUILD_TILE           = 128;   // output tile edge (m and n)
 constexpr int BUILD_CPA_THREADS    = 256;
-constexpr int BUILD_CPA_BK         = 16;    // k rows per staged slab
+#ifndef KM_CPA_BK
+#define KM_CPA_BK 32
+#endif
+constexpr int BUILD_CPA_BK         = KM_CPA_BK;   // k rows per staged slab
 constexpr int BUILD_CPA_STAGES     = 3;
 constexpr int BUILD_CPA_PITCH      = 132;   // floats per staged k row; 528 bytes keeps rows 16-byte aligned
 constexpr int BUILD_CPA_SMEM_BYTES = BUILD_CPA_STAGES * 2 * BUILD_CPA_BK * BUILD_CPA_PITCH * 4;

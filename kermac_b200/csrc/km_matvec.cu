@@ -99,8 +99,8 @@ __global__ void __launch_bounds__(MV_THREADS, 2) matvec_kernel(const __grid_cons
         const int chunk = it / ktiles, kt = it - chunk * ktiles;
         const int mc0   = m_begin + chunk * MV_TILE;
         float* st       = smem + (it % MV_STAGES) * MV_STAGE_FLOATS;
-        stage_operand<AVEC>(st, A + (long long)mc0 * p.a_sm, p.a_sm, p.a_sk, m_end - mc0, K, kt, tid);
-        stage_operand<BVEC>(st + MV_BK * MV_PITCH, B, p.b_sn, p.b_sk, rem_n, K, kt, tid);
+        stage_operand<AVEC, MV_BK>(st, A + (long long)mc0 * p.a_sm, p.a_sm, p.a_sk, m_end - mc0, K, kt, tid);
+        stage_operand<BVEC, MV_BK>(st + MV_BK * MV_PITCH, B, p.b_sn, p.b_sk, rem_n, K, kt, tid);
     };
 
     if (total > 0) stage(0);
