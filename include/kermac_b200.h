@@ -102,6 +102,11 @@ typedef struct KmBuildArgs {
     int32_t reg_off_x, reg_off_y;
     float   epsilon;          /* used when kernel_type != KM_KERNEL_NONE */
     int32_t variant;          /* 0 = automatic; otherwise force a kernel variant (KM_VARIANT_*) */
+    int32_t out_multicast;    /* 0: `out` is ordinary device memory.  1: `out` is the multicast address of an
+                                 NVSwitch multicast object that every GPU of the group has bound to its own result
+                                 buffer (e.g. torch symmetric memory's multicast_ptr): results are written with
+                                 multimem.st, so each GPU's buffer receives them while the kernel computes.  The
+                                 caller synchronises the GPUs afterwards.  No reference counterpart. */
 } KmBuildArgs;
 
 /* Kernel variants of kermac_b200_build_kernel (for benchmarks and tests). */

@@ -52,6 +52,7 @@ class KmBuildArgs(C.Structure):
         ("reg_off_x", C.c_int32), ("reg_off_y", C.c_int32),
         ("epsilon", C.c_float),
         ("variant", C.c_int32),
+        ("out_multicast", C.c_int32),
     ]
 
 

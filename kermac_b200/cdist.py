@@ -41,15 +41,18 @@ def cdist(
         TypeError: inputs are not float32 torch tensors.
         ValueError: shapes, strides, batch sizes or devices are invalid.
     """
+    descriptor, powers = descriptor_for(p, skip_epilogue)
+    return run_kernel(descriptor, a, b, out=out, try_to_align=try_to_align, debug=debug, **powers)
+
+
+def descriptor_for(p: float, skip_epilogue: bool = False):
+    """(KernelDescriptor, power keyword arguments of run_kernel) that `cdist` uses for this p.
+    A fresh descriptor every time: nothing shared is modified."""
     if p == 1.0:
-        descriptor = KernelDescriptor(InnerOperator.DIFF, PowerType.ABS, PowerType.NOOP, KernelType.NONE)
-        return run_kernel(descriptor, a, b, out=out, try_to_align=try_to_align, debug=debug)
+        return KernelDescriptor(InnerOperator.DIFF, PowerType.ABS, PowerType.NOOP, KernelType.NONE), {}
     if p == 2.0:
         outer = PowerType.NOOP if skip_epilogue else PowerType.SQRT
-        descriptor = KernelDescriptor(InnerOperator.DIFF, PowerType.SQUARE, outer, KernelType.NONE)
-        return run_kernel(descriptor, a, b, out=out, try_to_align=try_to_align, debug=debug)
+        return KernelDescriptor(InnerOperator.DIFF, PowerType.SQUARE, outer, KernelType.NONE), {}
     if skip_epilogue:
-        descriptor = KernelDescriptor(InnerOperator.DIFF, PowerType.POW, PowerType.NOOP, KernelType.NONE)
-        return run_kernel(descriptor, a, b, out=out, inner_p=p, try_to_align=try_to_align, debug=debug)
-    descriptor = KernelDescriptor(InnerOperator.DIFF, PowerType.POW, PowerType.POW, KernelType.NONE)
-    return run_kernel(descriptor, a, b, out=out, p=p, try_to_align=try_to_align, debug=debug)
+        return KernelDescriptor(InnerOperator.DIFF, PowerType.POW, PowerType.NOOP, KernelType.NONE), {"inner_p": p}
+    return KernelDescriptor(InnerOperator.DIFF, PowerType.POW, PowerType.POW, KernelType.NONE), {"p": p}

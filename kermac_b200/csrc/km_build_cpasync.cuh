@@ -98,11 +98,11 @@ __device__ __forceinline__ void finish_block(const BuildParams& p, int l, u64 (&
                 v[e] = x;
             }
             if (p.c_vec4 && m + 3 < p.M) {
-                *reinterpret_cast<float4*>(row + m) = make_float4(v[0], v[1], v[2], v[3]);
+                store_result4(row + m, v[0], v[1], v[2], v[3], p.c_multicast != 0);
             } else {
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                    if (m + e < p.M) row[m + e] = v[e];
+                    if (m + e < p.M) store_result1(row + m + e, v[e], p.c_multicast != 0);
             }
         }
     }

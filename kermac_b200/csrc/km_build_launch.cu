@@ -103,6 +103,9 @@ int make_plan(const KmBuildArgs* a, BuildPlan* plan) {
     p.panel          = 16;
     if ((long long)p.tiles_m * p.tiles_n > 0x7fffffffLL) return fail(KM_ERR_TOO_LARGE, "too many output tiles");
     p.c_vec4 = aligned16(p.C) && (p.c_ld % 4 == 0) && (p.c_sl % 4 == 0);
+    if (a->out_multicast != 0 && a->out_multicast != 1)
+        return fail(KM_ERR_BAD_ENUM, "out_multicast must be 0 or 1");
+    p.c_multicast = a->out_multicast;
 
     plan->avec = (p.a_sm == 1) && aligned16(p.A) && (p.a_sk % 4 == 0 || p.K <= 1) && (p.a_sl % 4 == 0);
     plan->bvec = (p.b_sn == 1) && aligned16(p.B) && (p.b_sk % 4 == 0 || p.K <= 1) && (p.b_sl % 4 == 0);

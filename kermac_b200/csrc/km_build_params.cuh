@@ -32,6 +32,7 @@ struct BuildParams {
     int   tiles_m, tiles_n;         // 128 x 128 output tiles
     int   panel;                    // rasterisation: n-tiles per panel
     int   c_vec4;                   // C rows may be written with 16-byte stores
+    int   c_multicast;              // C is an NVSwitch multicast address: write with multimem.st
 };
 
 // Maps a linear tile index to (tile_m, tile_n) so that thread blocks that run at

@@ -121,6 +121,26 @@ __device__ __forceinline__ void ex2_poly2(float x0, float x1, u64& r, u64& scale
     scale = pack2(__int_as_float(__float_as_int(t0) << 23), __int_as_float(__float_as_int(t1) << 23));
 }
 
+// ---------------------------------------------------------------- result stores
+// Ordinary stores, or multimem.st to an NVSwitch multicast address: one store that the
+// switch delivers to the same offset of every GPU bound to the multicast object.
+__device__ __forceinline__ void store_result4(float* dst, float v0, float v1, float v2, float v3, bool multicast) {
+    if (multicast) {
+        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v0), "f"(v1),
+                     "f"(v2), "f"(v3)
+                     : "memory");
+    } else {
+        *reinterpret_cast<float4*>(dst) = make_float4(v0, v1, v2, v3);
+    }
+}
+__device__ __forceinline__ void store_result1(float* dst, float v, bool multicast) {
+    if (multicast) {
+        asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(dst), "f"(v) : "memory");
+    } else {
+        *dst = v;
+    }
+}
+
 // ---------------------------------------------------------------- async copies
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

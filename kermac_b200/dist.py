@@ -133,14 +133,19 @@ class OverlappedCdist:
     SM's register file, so a communication kernel only gets to run between launches.)
 
     The result buffer is symmetric memory (`torch.distributed._symmetric_memory`), allocated
-    and exchanged once per object and reused by every `run`.  With `transport="collective"`,
-    or when the tensors are not on CUDA, the slabs are exchanged by one in-place all-gather
-    after the last launch instead.
+    and exchanged once per object and reused by every `run`.  Transports:
+      "multicast"  (default on CUDA when the NVSwitch multicast object is available) the kernel
+                   itself writes its results to the buffer's multicast address with multimem.st,
+                   so the switch delivers every row to all GPUs while the kernel computes: one
+                   kernel does the computation and the exchange, each GPU sends its slab once;
+      "peer_copy"  finished rows are pushed to each peer by copy engines (world - 1 copies of
+                   the slab leave every GPU; at 8 GPUs that takes as long as the computation);
+      "collective" one in-place all-gather after the last launch (also the CPU / Gloo path).
     """
 
     def __init__(self, M: int, N: int, device, group=None, chunks: int = 8, transport: str = "auto"):
-        if transport not in ("auto", "peer_copy", "collective"):
-            raise ValueError("transport must be 'auto', 'peer_copy' or 'collective'")
+        if transport not in ("auto", "multicast", "peer_copy", "collective"):
+            raise ValueError("transport must be 'auto', 'multicast', 'peer_copy' or 'collective'")
         device = torch.device(device)
         self.group = group
         self.world = dist_.get_world_size(group) if dist_.is_initialized() else 1
@@ -151,19 +156,28 @@ class OverlappedCdist:
         self.start = sum(self.sizes[:self.rank])
         self.rows = self.sizes[self.rank]
         self.chunks = max(1, chunks)
-        if transport == "auto":
-            transport = "peer_copy" if (device.type == "cuda" and self.world > 1) else "collective"
-        self.transport = transport
+        symmetric = device.type == "cuda" and self.world > 1 and transport != "collective"
         shape = (self.world * self.slab_rows, M)
         self._handle, self._peers, self._streams, self._second = None, None, None, None
-        if transport == "peer_copy":
+        self.launch_count = 0              # distance-kernel launches issued by this object so far
+        if symmetric:
             import torch.distributed._symmetric_memory as symm_mem
             self.full = symm_mem.empty(shape, dtype=torch.float32, device=device)
             self._handle = symm_mem.rendezvous(self.full, group=dist_.group.WORLD if group is None else group)
-            self._peers = [self._handle.get_buffer(r, shape, torch.float32) for r in range(self.world)]
-            self._streams = [torch.cuda.Stream(device=device) for _ in range(self.world)]
+            has_multicast = bool(getattr(self._handle, "multicast_ptr", 0))
+            if transport == "multicast" and not has_multicast:
+                raise RuntimeError("this group has no NVSwitch multicast object for symmetric memory")
+            if transport == "auto":
+                transport = "multicast" if has_multicast else "peer_copy"
+            if transport == "peer_copy":
+                self._peers = [self._handle.get_buffer(r, shape, torch.float32) for r in range(self.world)]
+                self._streams = [torch.cuda.Stream(device=device) for _ in range(self.world)]
         else:
+            if transport in ("multicast", "peer_copy") and self.world > 1:
+                raise RuntimeError(f"transport {transport!r} needs CUDA tensors")
+            transport = "collective"
             self.full = torch.empty(shape, dtype=torch.float32, device=device)
+        self.transport = transport
 
     def chunk_bounds(self):
         """[(row0, row1)] of the launches inside this rank's slab, on 128-row boundaries."""
@@ -182,6 +196,8 @@ class OverlappedCdist:
 
             def compute(a_, b_, out):
                 return _cdist(a_, b_, out=out, p=p, skip_epilogue=skip_epilogue)
+        if gather and self.world > 1 and self.transport == "multicast":
+            return self._run_multicast(a, b, p, skip_epilogue)
         push = gather and self.world > 1 and self.transport == "peer_copy"
         on_cuda = self.full.is_cuda
         main = torch.cuda.current_stream() if on_cuda else None
@@ -205,6 +221,7 @@ class OverlappedCdist:
             else:
                 with torch.cuda.stream(stream):
                     compute(a, b[rows], self.full[rows].t())
+            self.launch_count += 1
             if push:
                 done = torch.cuda.Event()
                 done.record(stream)
@@ -225,6 +242,30 @@ class OverlappedCdist:
         elif gather and self.world > 1:
             gather_rows_inplace(self.full, self.N, self.group)
         return self.full[:self.N]
+
+
+def _overlapped_run_multicast(self, a, b, p, skip_epilogue):
+    """One launch over this rank's slab whose result stores go to the multicast address of the
+    symmetric buffer: every GPU's buffer receives the rows while the kernel runs."""
+    from . import _native
+    from .build_a_kernel import _current_stream_for, _marshal_build
+    from .cdist import descriptor_for
+    self._handle.barrier()              # nobody is still reading the rows about to be overwritten
+    if self.rows > 0:
+        rows = slice(self.start, self.start + self.rows)
+        descriptor, powers = descriptor_for(p, skip_epilogue)
+        args, _, keep = _marshal_build(descriptor, a, b[rows], self.full[rows].t(), powers.get("p"),
+                                       powers.get("inner_p"), None, None, None, None, 0, 0)
+        args.out = self._handle.multicast_ptr + self.start * self.M * 4
+        args.out_multicast = 1
+        _native.launch_build(args, _current_stream_for(a.device))
+        self.launch_count += 1
+        del keep
+    self._handle.barrier()              # every rank's kernel, and with it its multicast stores, is complete
+    return self.full[:self.N]
+
+
+OverlappedCdist._run_multicast = _overlapped_run_multicast
 
 
 def kernel_matvec_sharded(kernel_descriptor, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,

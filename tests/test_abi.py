@@ -35,7 +35,7 @@ def test_every_declared_entry_point_is_exported():
 def test_struct_sizes_match_the_header_layout():
     # natural alignment of the C structs (int32 x4, then pointer/int64 runs, ...)
     assert ctypes.sizeof(_native.KmHyper) == 24
-    assert ctypes.sizeof(_native.KmBuildArgs) == 16 + 3 * 32 + 16 + 4 * 24 + 16
+    assert ctypes.sizeof(_native.KmBuildArgs) == 16 + 3 * 32 + 16 + 4 * 24 + 16 + 8
     assert ctypes.sizeof(_native.KmGradArgs) == 24 + 4 * 24 + 32 + 8 + 24 + 16 + 8
     assert ctypes.sizeof(_native.KmMatvecArgs) == 24 + 2 * 32 + 24 + 32 + 16 + 3 * 24 + 8 + 16 + 8
 
@@ -60,6 +60,7 @@ def _build_args(**kw):
     (dict(outer_power=9), -4),
     (dict(kernel_type=-1), -4),
     (dict(variant=5), -4),
+    (dict(out_multicast=2), -4),
     (dict(a_stride_m=3, a_stride_k=2), -3),
     (dict(out_stride_m=2, out_stride_n=3), -3),
     (dict(a_stride_l=-1), -3),

@@ -36,7 +36,7 @@ def _worker(rank, world, port, results):
             single = torch.empty(1000, 700, device="cuda")
             kermac.cdist(a, b, out=single.t(), p=p)
             ok = ok and torch.equal(full, single)                 # sharding must not change a single bit
-        for transport in ("peer_copy", "collective"):
+        for transport in ("multicast", "peer_copy", "collective"):
             ov = kdist.OverlappedCdist(700, 1000, torch.device("cuda", rank), chunks=3, transport=transport)
             for p in (1.0, 2.0, 1.3):
                 single = torch.empty(1000, 700, device="cuda")
