@@ -42,7 +42,7 @@
 extern "C" {
 #endif
 
-#define KERMAC_B200_ABI_VERSION 1
+#define KERMAC_B200_ABI_VERSION 2
 
 /* Rejected preconditions (negative return codes). */
 #define KM_ERR_NULL_POINTER   (-1)
@@ -174,7 +174,16 @@ int kermac_b200_cdist_grad_static(const KmGradArgs* args, void* stream);
  * c is m-contiguous: c[l][o][m] = c[l * c_stride_l + o * ldc + m].
  * y[l][n][o] = y[l * y_stride_l + n * y_stride_n + o * y_stride_o].
  * The diagonal regularisation rule does not apply here.
+ *
+ * contraction selects where the coefficient product runs: KM_CONTRACT_TENSOR (and
+ * KM_CONTRACT_AUTO) on the tcgen05 tensor cores as three tf32 products per term
+ * (operands split into a tf32 head and an fp32 remainder, fp32 accumulation: fp32-level
+ * accuracy), KM_CONTRACT_FP32 as packed FP32 FMAs.  The kernel-matrix values are
+ * computed in FP32 either way.
  */
+#define KM_CONTRACT_AUTO   0
+#define KM_CONTRACT_FP32   1
+#define KM_CONTRACT_TENSOR 2
 typedef struct KmMatvecArgs {
     int32_t m, n, k, o, l;
     const float* a; int64_t a_stride_m, a_stride_k, a_stride_l;
@@ -186,6 +195,7 @@ typedef struct KmMatvecArgs {
     float   epsilon;
     void*   scratch; int64_t scratch_bytes;
     int32_t split_m;          /* 0 = automatic (1 when scratch is NULL) */
+    int32_t contraction;      /* KM_CONTRACT_* */
 } KmMatvecArgs;
 
 int kermac_b200_kernel_matvec(const KmMatvecArgs* args, void* stream);

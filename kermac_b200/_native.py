@@ -11,7 +11,7 @@ import os
 import threading
 from typing import Optional
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 # enum values of include/kermac_b200.h
 INNER_DIFF, INNER_DOT = 0, 1
@@ -84,6 +84,7 @@ class KmMatvecArgs(C.Structure):
         ("epsilon", C.c_float),
         ("scratch", C.c_void_p), ("scratch_bytes", C.c_int64),
         ("split_m", C.c_int32),
+        ("contraction", C.c_int32),
     ]
 
 

@@ -23,6 +23,7 @@
 
 #include "km_build_cpasync.cuh"
 #include "km_build_tma.cuh"
+#include "km_mbar.cuh"
 #include "km_host.h"
 
 namespace km {
@@ -35,33 +36,6 @@ constexpr int TMA_TILE    = 128;
 constexpr int TMA_THREADS = 256;
 constexpr int TMA_WARPS   = TMA_THREADS / 32;
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, int bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, int parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-// Waits for the phase of `bar` with the given parity; gives up after a bounded
-// number of attempts (seconds at most) and returns false.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, int parity) {
-    for (int i = 0; i < (1 << 22); ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
@@ -310,5 +284,7 @@ extern "C" int kermac_b200_device_error_flag(void) {
     if (int rc = km::cuda_status(cudaDeviceSynchronize(), "cudaDeviceSynchronize")) return rc < 0 ? rc : -rc;
     if (km::cuda_status(cudaMemcpyFromSymbol(&v, km::g_tma_wait_expired, sizeof(int)), "cudaMemcpyFromSymbol")) return KM_ERR_INTERNAL;
     if (v) cudaMemcpyToSymbol(km::g_tma_wait_expired, &zero, sizeof(int));
-    return v ? 1 : 0;
+    const int mv = km::matvec_take_wait_flag();
+    if (mv < 0) return KM_ERR_INTERNAL;
+    return (v || mv) ? 1 : 0;
 }

@@ -192,6 +192,56 @@ struct Epilogue {
     }
 };
 
+// The same chain with the outer power and the kernel function known at compile time.
+template <int OP, int KT>
+__device__ __forceinline__ float epilogue_value(const Epilogue& e, float acc) {
+    if constexpr (OP == KM_POW_ABS) acc = fabsf(acc);
+    else if constexpr (OP == KM_POW_SQUARE) acc = acc * acc;
+    else if constexpr (OP == KM_POW_SQRT) acc = sqrt_approx(acc);
+    else if constexpr (OP == KM_POW_POW) acc = pow_approx(acc, e.p_outer);
+    if constexpr (KT != KM_KERNEL_NONE) {
+        if (acc < e.epsilon) acc = 0.0f;
+        acc = exp_approx(acc * e.neg_gamma);
+    }
+    return acc;
+}
+
+template <int OP, int KT>
+__device__ __forceinline__ void epilogue_columns(const Epilogue& e, u64 (&acc)[8][4], int first, int count) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (i < first || i >= first + count) continue;
+            float v0, v1;
+            unpack2(acc[j][i], v0, v1);
+            acc[j][i] = pack2(epilogue_value<OP, KT>(e, v0), epilogue_value<OP, KT>(e, v1));
+        }
+}
+
+// Applies the chain in place to the packed columns [first, first + count) of a thread's
+// 8 x 8 block.  The common chains get straight-line code (the choice is made once per
+// call, not once per value); every other combination takes the generic path.  All paths
+// compute the same values as Epilogue::operator().
+__device__ __forceinline__ void apply_epilogue(const Epilogue& e, u64 (&acc)[8][4], int first, int count) {
+    const int op = e.outer_power, kt = e.kernel_type;
+    if (op == KM_POW_SQRT && kt == KM_KERNEL_LAPLACE) epilogue_columns<KM_POW_SQRT, KM_KERNEL_LAPLACE>(e, acc, first, count);
+    else if (op == KM_POW_NOOP && kt == KM_KERNEL_LAPLACE) epilogue_columns<KM_POW_NOOP, KM_KERNEL_LAPLACE>(e, acc, first, count);
+    else if (op == KM_POW_NOOP && kt == KM_KERNEL_GAUSSIAN) epilogue_columns<KM_POW_NOOP, KM_KERNEL_GAUSSIAN>(e, acc, first, count);
+    else if (op == KM_POW_NOOP && kt == KM_KERNEL_NONE) { /* identity */ }
+    else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (i < first || i >= first + count) continue;
+                float v0, v1;
+                unpack2(acc[j][i], v0, v1);
+                acc[j][i] = pack2(e(v0), e(v1));
+            }
+    }
+}
+
 __device__ __forceinline__ Epilogue make_epilogue(int outer_power, int kernel_type, const KmHyper& p_outer,
                                                   const KmHyper& bandwidth, float epsilon, int l) {
     Epilogue e;

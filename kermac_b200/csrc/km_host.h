@@ -23,6 +23,10 @@ int require_sm100();
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Reads back and clears the wait-ran-out flag of the tensor-core matvec kernel
+// (km_matvec.cu); the device must already be synchronised.  0 / 1, or -1 on error.
+int matvec_take_wait_flag();
+
 inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

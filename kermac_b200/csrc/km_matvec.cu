@@ -15,6 +15,8 @@
 // (src/kermac/build_a_kernel.py:158-394) and multiply afterwards.
 #include "km_build_cpasync.cuh"
 #include "km_host.h"
+#include "km_mbar.cuh"
+#include "km_tcgen05.cuh"
 
 namespace km {
 namespace {
@@ -121,6 +123,8 @@ __global__ void __launch_bounds__(MV_THREADS, 2) matvec_kernel(const __grid_cons
             const int mc0 = m_begin + chunk * MV_TILE;
             // kernel-matrix values of this chunk -> shared memory, [n][m]; columns of
             // m outside the range are zeroed so they add nothing.
+            apply_epilogue(epi, acc, 0, 4);
+            const bool partial = (mc0 + MV_TILE > m_end);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const int nn = tn_off + (j >> 2) * 16 + (j & 3);
@@ -130,8 +134,10 @@ __global__ void __launch_bounds__(MV_THREADS, 2) matvec_kernel(const __grid_cons
                     float v[4];
                     unpack2(acc[j][2 * h], v[0], v[1]);
                     unpack2(acc[j][2 * h + 1], v[2], v[3]);
+                    if (partial) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) v[e] = (mc0 + mm + e < m_end) ? epi(v[e]) : 0.0f;
+                        for (int e = 0; e < 4; ++e) v[e] = (mc0 + mm + e < m_end) ? v[e] : 0.0f;
+                    }
                     *reinterpret_cast<float4*>(s_kt + nn * MV_KT_PITCH + mm) = make_float4(v[0], v[1], v[2], v[3]);
                     acc[j][2 * h] = acc[j][2 * h + 1] = 0ull;
                 }
@@ -191,6 +197,265 @@ __global__ void __launch_bounds__(MV_THREADS, 2) matvec_kernel(const __grid_cons
     }
 }
 
+// ---------------------------------------------------------------------------
+// Tensor-core contraction.  Same walk as matvec_kernel, but the coefficient product
+// of each 128 (n) x 128 (m) kernel-matrix tile runs on the 5th-generation tensor
+// cores: D[n, o] (128 x 16, fp32, in tensor memory) += Ktile[n, m] * c[o, m]^T with
+// tcgen05.mma kind::tf32 reading both operands from shared memory.
+//
+// fp32 accuracy is kept by splitting every operand value x into hi = x with the 13
+// low mantissa bits cleared (exactly representable in tf32) and lo = x - hi, and
+// issuing three products per k-block: hi*c_hi + lo*c_hi + hi*c_lo (the dropped
+// lo*c_lo term is below 2^-22 of the product).
+//
+// A tile is contracted in two rounds of 64 m-columns (the columns a thread holds in
+// its accumulator halves h = 0, 1), so that hi and lo of a round fit in 64 KiB.
+// Operand tiles use the K-major 128-byte-swizzle layout (see km_tcgen05.cuh): 32
+// floats per 128-byte row, one slab of rows per 32 m-columns.
+//
+// The tensor core truncates when it adds into its fp32 accumulator, so a long chain
+// of MMAs drifts low (measured: 5e-6 relative after 48 steps on same-sign data).
+// Chains are therefore kept short: per tile, each round's hi*c_hi products (8 MMAs)
+// have their own 16-column accumulator and the two correction products share a third,
+// whose truncation is relative to sums 2^-11 smaller.  The three partial sums are
+// added, rounding to nearest, to the thread's fp32 running sums one tile later, when
+// the tile's MMAs are known to be complete (two sets of accumulators alternate).
+// One mbarrier tracks MMA completion (tcgen05.commit); every wait on it is bounded.
+constexpr int MT_OT         = 16;
+constexpr int MT_SLAB_A     = 128 * 128;              // bytes: 128 rows (n) of 32 floats
+constexpr int MT_SLAB_B     = MT_OT * 128;            // bytes: 16 rows (o) of 32 floats
+constexpr int MT_A_BYTES    = 2 * MT_SLAB_A;          // one round: 64 m-columns
+constexpr int MT_B_BYTES    = 2 * MT_SLAB_B;
+constexpr int MT_OFF_A_HI   = 0;
+constexpr int MT_OFF_A_LO   = MT_A_BYTES;
+constexpr int MT_OFF_B_HI   = 2 * MT_A_BYTES;
+constexpr int MT_OFF_B_LO   = 2 * MT_A_BYTES + MT_B_BYTES;
+constexpr int MT_TILE_BYTES = 2 * MT_A_BYTES + 2 * MT_B_BYTES;
+constexpr int MT_SMEM_BYTES = 1024 + MT_TILE_BYTES + MV_STAGES * MV_STAGE_FLOATS * 4;
+constexpr int MT_TMEM_SET   = 64;                     // columns per tile: main h=0, main h=1, corrections, (unused)
+constexpr int MT_TMEM_COLS  = 2 * MT_TMEM_SET;
+static_assert(MT_TILE_BYTES % 1024 == 0 && MT_SLAB_B % 1024 == 0, "operand slabs must stay 1024-byte aligned");
+
+__device__ int g_matvec_wait_expired = 0;
+
+__device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
+
+template <int INNER, bool AVEC, bool BVEC>
+__global__ void __launch_bounds__(MV_THREADS, 2) matvec_tensor_kernel(const __grid_constant__ MatvecParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long s_bar;
+    __shared__ uint32_t s_tmem;
+
+    const uint32_t raw_addr  = smem_u32(smem_raw);
+    const uint32_t tile_addr = (raw_addr + 1023u) & ~1023u;          // operand tiles, 1024-byte aligned
+    unsigned char* tiles     = smem_raw + (tile_addr - raw_addr);
+    float* stages            = reinterpret_cast<float*>(tiles + MT_TILE_BYTES);
+    const uint32_t bar       = smem_u32(&s_bar);
+
+    const int tid  = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int tn    = blockIdx.x % p.tiles_n;
+    const int split = blockIdx.x / p.tiles_n;
+    const int oc    = blockIdx.y;
+    const int l     = blockIdx.z;
+    const int n0 = tn * MV_TILE;
+    const int o0 = oc * MT_OT;
+    const int m_begin = split * p.m_per_split;
+    const int m_end   = min(p.M, m_begin + p.m_per_split);
+    const int chunks  = (m_end > m_begin) ? (m_end - m_begin + MV_TILE - 1) / MV_TILE : 0;
+
+    const float* A = p.A + (long long)l * p.a_sl;
+    const float* B = p.B + (long long)l * p.b_sl + (long long)n0 * p.b_sn;
+    const float* C = p.C + (long long)l * p.c_sl;
+    const int rem_n = p.N - n0;
+    const int K = p.K;
+    const int ktiles = K > 0 ? (K + MV_BK - 1) / MV_BK : 1;
+    const int total  = chunks * ktiles;
+
+    const float p_inner = (INNER == IN_DIFF_POW || INNER == IN_DOT_POW) ? read_hyper(p.p_inner, l) : 0.0f;
+    const Epilogue epi  = make_epilogue(p.outer_power, p.kernel_type, p.p_outer, p.bandwidth, p.epsilon, l);
+
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        tc::fence_smem_to_async();
+    }
+    if (warp == 0) tc::tmem_alloc(smem_u32(&s_tmem), MT_TMEM_COLS);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem = s_tmem;
+
+    const int lm = lane & 7, ln = lane >> 3;
+    const int wm = warp & 1, wn = warp >> 1;
+    const int tm_off = wm * 64 + lm * 4;
+    const int tn_off = wn * 32 + ln * 4;
+
+    // read-back role: row cn of the tile, channels ch * 8 .. ch * 8 + 7
+    const int cn = tid & (MV_TILE - 1);
+    const int ch = tid >> 7;
+    const uint32_t tmem_mine = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + ch * 8;
+    float yacc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) yacc[i] = 0.0f;
+
+    // coefficient staging role: channel co, 16-byte chunk cq of the round's 64 columns
+    const int co = tid >> 4;
+    const int cq = tid & 15;
+
+    u64 acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0ull;
+
+    bool pending = false;   // a commit has been issued that nobody has waited for yet
+    int  parity  = 0;
+    bool expired = false;
+    auto wait_mma = [&]() {
+        if (pending) {
+            // once a wait has run out this thread stops waiting, so a stuck barrier costs one limit, not one per tile
+            if (!expired && !mbar_wait_bounded(bar, parity)) expired = true;
+            parity ^= 1;
+            pending = false;
+        }
+    };
+    auto drain = [&](int buffer) {
+        tc::fence_after_sync();
+#pragma unroll
+        for (int part = 0; part < 3; ++part) {
+            uint32_t r[8];
+            tc::ld_32x32b_x8(tmem_mine + buffer * MT_TMEM_SET + part * MT_OT, r);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) yacc[i] += __uint_as_float(r[i]);
+        }
+        tc::fence_before_sync();
+    };
+
+    auto stage = [&](int it) {
+        const int chunk = it / ktiles, kt = it - chunk * ktiles;
+        const int mc0   = m_begin + chunk * MV_TILE;
+        float* st       = stages + (it % MV_STAGES) * MV_STAGE_FLOATS;
+        stage_operand<AVEC, MV_BK>(st, A + (long long)mc0 * p.a_sm, p.a_sm, p.a_sk, m_end - mc0, K, kt, tid);
+        stage_operand<BVEC, MV_BK>(st + MV_BK * MV_PITCH, B, p.b_sn, p.b_sk, rem_n, K, kt, tid);
+    };
+
+    if (total > 0) stage(0);
+    cp_async_commit();
+
+    for (int it = 0; it < total; ++it) {
+        const int chunk = it / ktiles, kt = it - chunk * ktiles;
+        cp_async_wait<0>();
+        __syncthreads();
+        if (it + 1 < total) stage(it + 1);
+        cp_async_commit();
+
+        const float* sa = stages + (it % MV_STAGES) * MV_STAGE_FLOATS + tm_off;
+        const float* sb = stages + (it % MV_STAGES) * MV_STAGE_FLOATS + MV_BK * MV_PITCH + tn_off;
+        consume_slab<INNER, MV_BK, MV_PITCH>(acc, sa, sb, K - kt * MV_BK, p_inner, 1.0f);
+
+        if (kt == ktiles - 1) {
+            const int mc0 = m_begin + chunk * MV_TILE;
+            const uint32_t d_set = tmem + (chunk & 1) * MT_TMEM_SET;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                // outer chain of this round's 32 values, in place; in the last, partial tile of the m
+                // range the columns outside it become 0
+                apply_epilogue(epi, acc, 2 * h, 2);
+                if (mc0 + MV_TILE > m_end) {
+                    const int mcol = mc0 + tm_off + h * 32;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float v[4];
+                        unpack2(acc[j][2 * h], v[0], v[1]);
+                        unpack2(acc[j][2 * h + 1], v[2], v[3]);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) v[e] = (mcol + e < m_end) ? v[e] : 0.0f;
+                        acc[j][2 * h]     = pack2(v[0], v[1]);
+                        acc[j][2 * h + 1] = pack2(v[2], v[3]);
+                    }
+                }
+                // this thread's four coefficients of the round: local column q <-> m = mc0 + (q / 32) * 64 + h * 32 + q % 32
+                float cv[4];
+                {
+                    const int q  = cq * 4;
+                    const int mg = mc0 + (q >> 5) * 64 + h * 32 + (q & 31);
+                    const bool o_ok = (o0 + co < p.O);
+                    const float* crow = C + (long long)(o0 + co) * p.ldc;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) cv[e] = (o_ok && mg + e < m_end) ? crow[mg + e] : 0.0f;
+                }
+                // the previous round's MMAs must have finished reading the operand tiles
+                wait_mma();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int r = tn_off + (j >> 2) * 16 + (j & 3);
+                    float v[4];
+                    unpack2(acc[j][2 * h], v[0], v[1]);
+                    unpack2(acc[j][2 * h + 1], v[2], v[3]);
+                    float hi[4], lo[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { hi[e] = tf32_hi(v[e]); lo[e] = v[e] - hi[e]; }
+                    const int off = wm * MT_SLAB_A + r * 128 + ((lm ^ (r & 7)) << 4);
+                    *reinterpret_cast<float4*>(tiles + MT_OFF_A_HI + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<float4*>(tiles + MT_OFF_A_LO + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+                    acc[j][2 * h] = acc[j][2 * h + 1] = 0ull;
+                }
+                {
+                    float hi[4], lo[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { hi[e] = tf32_hi(cv[e]); lo[e] = cv[e] - hi[e]; }
+                    const int off = (cq >> 3) * MT_SLAB_B + co * 128 + (((cq & 7) ^ (co & 7)) << 4);
+                    *reinterpret_cast<float4*>(tiles + MT_OFF_B_HI + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<float4*>(tiles + MT_OFF_B_LO + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+                }
+                tc::fence_smem_to_async();
+                tc::fence_before_sync();
+                __syncthreads();
+                if (tid == 0) {
+                    tc::fence_after_sync();
+                    constexpr uint32_t idesc = tc::instr_desc_tf32(MV_TILE, MT_OT);
+#pragma unroll
+                    for (int pass = 0; pass < 3; ++pass) {
+                        const uint32_t a_base = tile_addr + (pass == 1 ? MT_OFF_A_LO : MT_OFF_A_HI);
+                        const uint32_t b_base = tile_addr + (pass == 2 ? MT_OFF_B_LO : MT_OFF_B_HI);
+#pragma unroll
+                        for (int kb = 0; kb < 8; ++kb) {
+                            const uint64_t da = tc::smem_desc_k_major_sw128(a_base + (kb >> 2) * MT_SLAB_A + (kb & 3) * 32);
+                            const uint64_t db = tc::smem_desc_k_major_sw128(b_base + (kb >> 2) * MT_SLAB_B + (kb & 3) * 32);
+                            if (pass == 0) tc::mma_tf32(d_set + h * MT_OT, da, db, idesc, kb != 0);
+                            else           tc::mma_tf32(d_set + 2 * MT_OT, da, db, idesc, !(h == 0 && pass == 1 && kb == 0));
+                        }
+                    }
+                    tc::commit(bar);
+                }
+                pending = true;
+            }
+            // the tile before this one finished before this tile's first round started
+            if (chunk > 0) drain((chunk - 1) & 1);
+        }
+    }
+    cp_async_wait<0>();
+
+    wait_mma();
+    if (chunks > 0) drain((chunks - 1) & 1);
+    if (expired) atomicExch(&g_matvec_wait_expired, 1);
+
+    const int n = n0 + cn;
+    if (n < p.N && !expired) {
+        float* yrow = p.Y + (long long)split * p.split_stride + (long long)l * p.y_sl + (long long)n * p.y_sn;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int o = o0 + ch * 8 + i;
+            if (o < p.O) yrow[(long long)o * p.y_so] = yacc[i];
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tmem, MT_TMEM_COLS);
+}
+
 __global__ void __launch_bounds__(256) matvec_reduce_kernel(const float* __restrict__ partial, float* __restrict__ y,
                                                             int N, int O, int L, int splits, long long split_stride,
                                                             long long y_sn, long long y_so, long long y_sl) {
@@ -233,6 +498,22 @@ MatvecFn mv_pick(int inner, int ot, bool avec, bool bvec) {
     }
     return nullptr;
 }
+template <int INNER>
+MatvecFn mv_pick_tensor_layout(bool avec, bool bvec) {
+    if (avec && bvec) return matvec_tensor_kernel<INNER, true, true>;
+    if (avec) return matvec_tensor_kernel<INNER, true, false>;
+    if (bvec) return matvec_tensor_kernel<INNER, false, true>;
+    return matvec_tensor_kernel<INNER, false, false>;
+}
+MatvecFn mv_pick_tensor(int inner, bool avec, bool bvec) {
+    switch (inner) {
+        case IN_DIFF_ABS: return mv_pick_tensor_layout<IN_DIFF_ABS>(avec, bvec);
+        case IN_DIFF_SQUARE: return mv_pick_tensor_layout<IN_DIFF_SQUARE>(avec, bvec);
+        case IN_DIFF_POW: return mv_pick_tensor_layout<IN_DIFF_POW>(avec, bvec);
+        case IN_DOT_NOOP: return mv_pick_tensor_layout<IN_DOT_NOOP>(avec, bvec);
+    }
+    return nullptr;
+}
 int mv_smem_for(int ot) {
     switch (ot) {
         case 2: return mv_smem_bytes<2>();
@@ -251,6 +532,7 @@ struct MatvecPlan {
     MatvecParams p;
     int ot;
     bool avec, bvec;
+    bool tensor;              // contraction on the tensor cores (3 x tf32) instead of packed FP32
     int splits_wanted;
     long long partial_elems;
 };
@@ -277,6 +559,8 @@ int make_matvec_plan(const KmMatvecArgs* a, MatvecPlan* plan) {
     if (!hyper_ok(a->p_inner) || !hyper_ok(a->p_outer) || !hyper_ok(a->bandwidth))
         return fail(KM_ERR_BAD_HYPERPARAM, "hyper-parameter vectors need a non-negative batch stride");
     if (a->split_m < 0) return fail(KM_ERR_BAD_SHAPE, "split_m must be >= 0");
+    if (a->contraction < KM_CONTRACT_AUTO || a->contraction > KM_CONTRACT_TENSOR)
+        return fail(KM_ERR_BAD_ENUM, "contraction must be KM_CONTRACT_AUTO, _FP32 or _TENSOR");
 
     MatvecParams& p = plan->p;
     p.M = a->m; p.N = a->n; p.K = a->k; p.O = a->o; p.L = a->l;
@@ -290,8 +574,10 @@ int make_matvec_plan(const KmMatvecArgs* a, MatvecPlan* plan) {
     p.kernel_type = a->kernel_type;
     p.p_inner = a->p_inner; p.p_outer = a->p_outer; p.bandwidth = a->bandwidth;
     p.epsilon = a->epsilon;
+    plan->tensor = (a->contraction != KM_CONTRACT_FP32);
     int ot = 2;
     while (ot < a->o && ot < 16) ot *= 2;
+    if (plan->tensor) ot = MT_OT;
     plan->ot   = ot;
     p.tiles_n  = (int)ceil_div_ll(p.N, MV_TILE);
     p.o_chunks = (int)ceil_div_ll(p.O > 0 ? p.O : 1, ot);
@@ -323,6 +609,16 @@ int make_matvec_plan(const KmMatvecArgs* a, MatvecPlan* plan) {
 }
 
 }  // namespace
+}  // namespace km
+
+namespace km {
+// Reads back and clears the flag a bounded wait of matvec_tensor_kernel sets (device already synchronised).
+int matvec_take_wait_flag() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_matvec_wait_expired, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_matvec_wait_expired, &zero, sizeof(int));
+    return v ? 1 : 0;
+}
 }  // namespace km
 
 extern "C" int64_t kermac_b200_kernel_matvec_scratch_bytes(const KmMatvecArgs* args) {
@@ -366,9 +662,10 @@ extern "C" int kermac_b200_kernel_matvec(const KmMatvecArgs* args, void* stream)
         p.y_sn = args->y_stride_n; p.y_so = args->y_stride_o; p.y_sl = args->y_stride_l;
         p.split_stride = 0;
     }
-    MatvecFn fn = mv_pick(p.inner_id, plan.ot, plan.avec, plan.bvec);
+    MatvecFn fn = plan.tensor ? mv_pick_tensor(p.inner_id, plan.avec, plan.bvec)
+                              : mv_pick(p.inner_id, plan.ot, plan.avec, plan.bvec);
     if (!fn) return fail(KM_ERR_INTERNAL, "no matvec kernel for inner id %d", p.inner_id);
-    const int smem_bytes = mv_smem_for(plan.ot);
+    const int smem_bytes = plan.tensor ? MT_SMEM_BYTES : mv_smem_for(plan.ot);
     if (int rc = cuda_status(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes),
                              "cudaFuncSetAttribute(matvec_kernel)"))
         return rc;

@@ -1,0 +1,67 @@
+// Inline-PTX helpers for the 5th-generation tensor cores of sm_100a: tensor-memory
+// allocation, shared-memory matrix descriptors, tcgen05.mma (kind::tf32, one CTA),
+// commit to an mbarrier and accumulator read-back.
+#pragma once
+
+#include <cstdint>
+
+namespace km {
+namespace tc {
+
+// Shared-memory matrix descriptor of a K-major operand stored as 128-byte rows with
+// the 128-byte swizzle: row r of a slab lives at r * 128 bytes, and its 16-byte chunk c
+// is stored at chunk position c ^ (r % 8).  Slabs are 1024-byte aligned.  Fields:
+// start address >> 4 in bits [0,14), leading byte offset (1, unused by swizzled
+// K-major layouts) in [16,30), stride between 8-row groups (1024 bytes >> 4) in
+// [32,46), descriptor version 1 in [46,48), layout type 2 (128-byte swizzle) in [61,64).
+__device__ __forceinline__ uint64_t smem_desc_k_major_sw128(uint32_t smem_addr) {
+    return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor for D(f32) += A(tf32) * B(tf32), both operands K-major:
+// accumulator format f32 in bits [4,6), A and B format tf32 (2) in [7,10) and [10,13),
+// N >> 3 in [17,23), M >> 4 in [24,29).
+__host__ __device__ constexpr uint32_t instr_desc_tf32(int M, int N) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+// Executed by one whole warp.  Writes the allocation's base address to *dst_smem.
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Makes shared-memory writes of this thread visible to the asynchronous units.
+__device__ __forceinline__ void fence_smem_to_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// One thread issues D[tmem] (+)= A[smem] * B[smem].
+__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
+        : "memory");
+}
+// The mbarrier receives one arrival when every tcgen05.mma this thread issued before has completed.
+__device__ __forceinline__ void commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// Warp-wide: lane i reads 8 consecutive 32-bit columns of tensor-memory lane (taddr.lane + i).
+__device__ __forceinline__ void ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8]) {
+    // The wait is part of the same statement so that no use of r[] can be scheduled before it.
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr)
+        : "memory");
+}
+
+}  // namespace tc
+}  // namespace km

@@ -8,6 +8,7 @@ there once M x N no longer fits in memory.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Union
 
 import torch
@@ -92,6 +93,18 @@ def _marshal_matvec(kernel_descriptor, a, b, c, out, p, inner_p, outer_p, bandwi
     return args, out, (inner_p, outer_p, bandwidth)
 
 
+_CONTRACTIONS = {"auto": 0, "fp32": 1, "tensor": 2}
+
+
+def _contraction_code(name: Optional[str]) -> int:
+    if name is None:
+        name = os.environ.get("KERMAC_B200_CONTRACTION", "auto")
+    try:
+        return _CONTRACTIONS[str(name).lower()]
+    except KeyError:
+        raise ValueError(f"contraction must be one of {sorted(_CONTRACTIONS)}, got {name!r}") from None
+
+
 def kernel_matvec(
     kernel_descriptor: KernelDescriptor,
     a: torch.Tensor,
@@ -104,6 +117,7 @@ def kernel_matvec(
     bandwidth: Optional[Union[float, torch.Tensor]] = None,
     epsilon: Optional[float] = None,
     split_m: int = 0,
+    contraction: Optional[str] = None,
     debug=False,
 ):
     """y[l, n, o] = sum_m Kmat[l, m, n] * c[l, o, m], Kmat = run_kernel(kernel_descriptor, a, b, ...).
@@ -112,11 +126,15 @@ def kernel_matvec(
     m; out: (N, O) / (L, N, O), allocated as (L, N, O) when None.  Hyper-parameters as in
     `run_kernel`, without the diagonal regularisation.  `split_m` > 1 divides the sum over m
     among that many thread blocks per row tile (0 picks automatically); partial sums are
-    added in a fixed order, so the result does not depend on scheduling.
+    added in a fixed order, so the result does not depend on scheduling.  `contraction`
+    selects where the coefficient product runs: "tensor" (tcgen05 tensor cores, three tf32
+    products per term, fp32-level accuracy), "fp32" (packed FP32 FMAs) or "auto" / None
+    (the environment variable KERMAC_B200_CONTRACTION, else the library default: tensor).
     """
     args, out, keep_alive = _marshal_matvec(kernel_descriptor, a, b, c, out, p, inner_p, outer_p, bandwidth, epsilon)
     stream_ptr = _current_stream_for(a.device)
     args.split_m = int(split_m)
+    args.contraction = _contraction_code(contraction)
     need = int(_native.lib().kermac_b200_kernel_matvec_scratch_bytes(ctypes.byref(args)))
     scratch = None
     if need > 0:

@@ -1,14 +1,22 @@
 """GPU parity of the fused kernel_matvec against the float64 CPU oracle, through the C-ABI.
-Tolerance: max |y - ref| / max |ref| <= 5e-5."""
+Tolerance: max |y - ref| / max |ref| <= 5e-5.  Every test runs once per contraction mode
+(tcgen05 tensor cores with three tf32 products per term, and packed FP32 FMAs)."""
 import pytest
 import torch
 
 import kermac_b200 as kermac
+from kermac_b200 import _native
 from oracle import kermac_oracle as ko
 
 pytestmark = pytest.mark.gpu
 TOL = 5e-5
 LAPLACE_L2 = dict(inner_operator="DIFF", inner_power="SQUARE", outer_power="SQRT", kernel_type="LAPLACE")
+
+
+@pytest.fixture(autouse=True, params=["tensor", "fp32"])
+def contraction(request, monkeypatch):
+    monkeypatch.setenv("KERMAC_B200_CONTRACTION", request.param)
+    return request.param
 
 
 def gen(shape, seed):
@@ -95,3 +103,26 @@ def test_matvec_configuration_shape_sampled_rows():
     assert ko.rel_err_signed(y[rows.cuda()], ref) < TOL
     y2 = kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a.cuda(), b.cuda(), (2.0 * c).cuda(), bandwidth=8.0)[0]
     assert torch.equal(y2, 2.0 * y)          # scaling c by a power of two scales every partial sum exactly
+
+
+def test_tensor_contraction_keeps_fp32_accuracy():
+    # One tf32 product per term would be off by ~1e-4 .. 1e-3; the three-product split has to stay
+    # at the level of the FP32 contraction.  Coefficients of one sign: no cancellation hides errors.
+    M, N, K, O = 6000, 384, 32, 16
+    a, b = gen((M, K), 20), gen((N, K), 21)
+    c = gen((O, M), 22).abs() + 0.5
+    ref = ko.kernel_matvec_ref(a, b, c, **LAPLACE_L2, bandwidth=8.0)
+    errs = {}
+    for mode in ("tensor", "fp32"):
+        y = kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a.cuda(), b.cuda(), c.cuda(), bandwidth=8.0,
+                                 contraction=mode)
+        errs[mode] = ko.rel_err_nonneg(y, ref)
+    assert errs["fp32"] < 2e-6
+    assert errs["tensor"] < 2e-6, errs
+    assert _native.device_error_flag() == 0, "a bounded wait inside the kernel ran out"
+
+
+def test_contraction_argument_is_validated():
+    a, b, c = gen((8, 4), 1).cuda(), gen((8, 4), 2).cuda(), gen((2, 8), 3).cuda()
+    with pytest.raises(ValueError):
+        kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=1.0, contraction="bf16")
