@@ -36,13 +36,6 @@ constexpr int TMA_TILE    = 128;
 constexpr int TMA_THREADS = 256;
 constexpr int TMA_WARPS   = TMA_THREADS / 32;
 
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
-        : "memory");
-}
-
 template <int INNER, int BK, int STAGES, int LAG>
 __global__ void __launch_bounds__(TMA_THREADS, 2)
 build_tma_kernel(const __grid_constant__ BuildParams p, const __grid_constant__ CUtensorMap map_a,
@@ -232,6 +225,14 @@ TmaChoice tma_kernel(int inner) {
 }
 
 }  // namespace
+
+int encode_tma_operand(CUtensorMap* map, const float* base, int extent, int K, int L, long long s_k, long long s_l,
+                       int box_k) {
+    return encode_operand(map, base, extent, K, L, s_k, s_l, box_k);
+}
+bool tma_operand_ok(const float* base, long long s_t, long long s_k, long long s_l, int K, int L) {
+    return operand_tma_ok(base, s_t, s_k, s_l, K, L);
+}
 
 bool tma_supported(const BuildParams& p) {
     if (!tma_kernel(p.inner_id).fn) return false;

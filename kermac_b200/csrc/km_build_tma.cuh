@@ -1,6 +1,8 @@
 // Kernel-matrix build, TMA staged (declarations; implementation in km_build_tma.cu).
 #pragma once
 
+#include <cuda.h>
+
 #include "km_build_params.cuh"
 
 namespace km {
@@ -14,5 +16,12 @@ bool tma_supported(const BuildParams& p);
 bool tma_preferred(const BuildParams& p);
 
 int launch_build_tma(const BuildParams& p, cudaStream_t stream);
+
+// Describes one fp32 operand as a rank-3 tensor (tile dimension, k, batch) with a box of
+// 128 x box_k x 1 elements.  `map` is a CUtensorMap.  Returns 0 or a KM_ERR_* code.
+int encode_tma_operand(CUtensorMap* map, const float* base, int extent, int K, int L, long long s_k, long long s_l,
+                       int box_k);
+// True when an operand with these strides can be described that way.
+bool tma_operand_ok(const float* base, long long s_t, long long s_k, long long s_l, int K, int L);
 
 }  // namespace km

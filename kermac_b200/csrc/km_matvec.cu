@@ -13,7 +13,10 @@
 //
 // The reference has no such kernel: callers materialise run_kernel(...)
 // (src/kermac/build_a_kernel.py:158-394) and multiply afterwards.
+#include <cstring>
+
 #include "km_build_cpasync.cuh"
+#include "km_build_tma.cuh"
 #include "km_host.h"
 #include "km_mbar.cuh"
 #include "km_tcgen05.cuh"
@@ -240,10 +243,19 @@ __device__ int g_matvec_wait_expired = 0;
 
 __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
 
-template <int INNER, bool AVEC, bool BVEC>
-__global__ void __launch_bounds__(MV_THREADS, 2) matvec_tensor_kernel(const __grid_constant__ MatvecParams p) {
+//
+// Operand staging comes in two forms.  TMA = false: the 2-stage cp.async pipeline of
+// matvec_kernel (any layout).  TMA = true (operands contiguous along m / n, 16-byte
+// aligned): tiled TMA copies (no multicast) into a 2-stage ring with a full and an empty
+// mbarrier per stage, refilled by thread 0 one slab behind its own consumption, so the
+// k loop has no block-wide barrier and no per-thread copy instructions.
+template <int INNER, bool AVEC, bool BVEC, bool TMA>
+__global__ void __launch_bounds__(MV_THREADS, 2)
+matvec_tensor_kernel(const __grid_constant__ MatvecParams p, const __grid_constant__ CUtensorMap map_a,
+                     const __grid_constant__ CUtensorMap map_b) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long s_bar;
+    __shared__ __align__(8) unsigned long long s_ring[2 * MV_STAGES];   // full[0..], empty[0..]
     __shared__ uint32_t s_tmem;
 
     const uint32_t raw_addr  = smem_u32(smem_raw);
@@ -276,8 +288,18 @@ __global__ void __launch_bounds__(MV_THREADS, 2) matvec_tensor_kernel(const __gr
     const float p_inner = (INNER == IN_DIFF_POW || INNER == IN_DOT_POW) ? read_hyper(p.p_inner, l) : 0.0f;
     const Epilogue epi  = make_epilogue(p.outer_power, p.kernel_type, p.p_outer, p.bandwidth, p.epsilon, l);
 
+    const uint32_t ring = smem_u32(s_ring);
+    auto full_bar  = [&](int s) { return ring + 8u * s; };
+    auto empty_bar = [&](int s) { return ring + 8u * (MV_STAGES + s); };
     if (tid == 0) {
         mbar_init(bar, 1);
+        if constexpr (TMA) {
+#pragma unroll
+            for (int s = 0; s < MV_STAGES; ++s) {
+                mbar_init(full_bar(s), 1);
+                mbar_init(empty_bar(s), MV_THREADS / 32);
+            }
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         tc::fence_smem_to_async();
     }
@@ -333,27 +355,62 @@ __global__ void __launch_bounds__(MV_THREADS, 2) matvec_tensor_kernel(const __gr
         tc::fence_before_sync();
     };
 
+    constexpr int PITCH        = TMA ? MV_TILE : MV_PITCH;               // floats per staged k row
+    constexpr int STAGE_FLOATS = 2 * MV_BK * PITCH;
+    const int la = (p.a_sl == 0) ? 0 : l;   // broadcast operands have a single batch slice in their map
+    const int lb = (p.b_sl == 0) ? 0 : l;
+    int issued = 0;                         // slabs handed to the TMA engine so far (thread 0 only)
+
     auto stage = [&](int it) {
         const int chunk = it / ktiles, kt = it - chunk * ktiles;
         const int mc0   = m_begin + chunk * MV_TILE;
-        float* st       = stages + (it % MV_STAGES) * MV_STAGE_FLOATS;
-        stage_operand<AVEC, MV_BK>(st, A + (long long)mc0 * p.a_sm, p.a_sm, p.a_sk, m_end - mc0, K, kt, tid);
-        stage_operand<BVEC, MV_BK>(st + MV_BK * MV_PITCH, B, p.b_sn, p.b_sk, rem_n, K, kt, tid);
+        float* st       = stages + (it % MV_STAGES) * STAGE_FLOATS;
+        if constexpr (TMA) {
+            const int s        = it % MV_STAGES;
+            const uint32_t dst = smem_u32(st);
+            issued             = it + 1;
+            mbar_expect_tx(full_bar(s), STAGE_FLOATS * 4);
+            tma_load_3d(dst, &map_a, mc0, kt * MV_BK, la, full_bar(s));
+            tma_load_3d(dst + MV_BK * PITCH * 4, &map_b, n0, kt * MV_BK, lb, full_bar(s));
+        } else {
+            stage_operand<AVEC, MV_BK>(st, A + (long long)mc0 * p.a_sm, p.a_sm, p.a_sk, m_end - mc0, K, kt, tid);
+            stage_operand<BVEC, MV_BK>(st + MV_BK * MV_PITCH, B, p.b_sn, p.b_sk, rem_n, K, kt, tid);
+        }
     };
 
-    if (total > 0) stage(0);
-    cp_async_commit();
+    if constexpr (TMA) {
+        if (tid == 0)
+            for (int it = 0; it < MV_STAGES && it < total; ++it) stage(it);
+    } else {
+        if (total > 0) stage(0);
+        cp_async_commit();
+    }
 
     for (int it = 0; it < total; ++it) {
         const int chunk = it / ktiles, kt = it - chunk * ktiles;
-        cp_async_wait<0>();
-        __syncthreads();
-        if (it + 1 < total) stage(it + 1);
-        cp_async_commit();
+        const int s     = it % MV_STAGES;
+        if constexpr (TMA) {
+            // refill the stage of the previous slab once every warp has released it
+            if (tid == 0 && it >= 1 && it - 1 + MV_STAGES < total) {
+                const int done = it - 1;
+                if (!expired && !mbar_wait_bounded(empty_bar(done % MV_STAGES), (done / MV_STAGES) & 1)) expired = true;
+                if (!expired) stage(done + MV_STAGES);
+            }
+            if (!expired && !mbar_wait_bounded(full_bar(s), (it / MV_STAGES) & 1)) expired = true;
+        } else {
+            cp_async_wait<0>();
+            __syncthreads();
+            if (it + 1 < total) stage(it + 1);
+            cp_async_commit();
+        }
 
-        const float* sa = stages + (it % MV_STAGES) * MV_STAGE_FLOATS + tm_off;
-        const float* sb = stages + (it % MV_STAGES) * MV_STAGE_FLOATS + MV_BK * MV_PITCH + tn_off;
-        consume_slab<INNER, MV_BK, MV_PITCH>(acc, sa, sb, K - kt * MV_BK, p_inner, 1.0f);
+        const float* sa = stages + s * STAGE_FLOATS + tm_off;
+        const float* sb = stages + s * STAGE_FLOATS + MV_BK * PITCH + tn_off;
+        consume_slab<INNER, MV_BK, PITCH>(acc, sa, sb, K - kt * MV_BK, p_inner, 1.0f);
+        if constexpr (TMA) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_bar(s));
+        }
 
         if (kt == ktiles - 1) {
             const int mc0 = m_begin + chunk * MV_TILE;
@@ -440,7 +497,17 @@ __global__ void __launch_bounds__(MV_THREADS, 2) matvec_tensor_kernel(const __gr
 
     wait_mma();
     if (chunks > 0) drain((chunks - 1) & 1);
-    if (expired) atomicExch(&g_matvec_wait_expired, 1);
+    if (expired) {
+        atomicExch(&g_matvec_wait_expired, 1);
+        if constexpr (TMA) {
+            // give copies already handed to the TMA engine a bounded chance to land before
+            // this block's shared memory is released
+            if (tid == 0)
+                for (int slab = issued > MV_STAGES ? issued - MV_STAGES : 0; slab < issued; ++slab)
+                    for (int i = 0; i < (1 << 16); ++i)
+                        if (mbar_try_wait(full_bar(slab % MV_STAGES), (slab / MV_STAGES) & 1)) break;
+        }
+    }
 
     const int n = n0 + cn;
     if (n < p.N && !expired) {
@@ -498,19 +565,22 @@ MatvecFn mv_pick(int inner, int ot, bool avec, bool bvec) {
     }
     return nullptr;
 }
+typedef void (*MatvecTensorFn)(const MatvecParams, const CUtensorMap, const CUtensorMap);
+
 template <int INNER>
-MatvecFn mv_pick_tensor_layout(bool avec, bool bvec) {
-    if (avec && bvec) return matvec_tensor_kernel<INNER, true, true>;
-    if (avec) return matvec_tensor_kernel<INNER, true, false>;
-    if (bvec) return matvec_tensor_kernel<INNER, false, true>;
-    return matvec_tensor_kernel<INNER, false, false>;
+MatvecTensorFn mv_pick_tensor_layout(bool avec, bool bvec, bool tma) {
+    if (tma) return matvec_tensor_kernel<INNER, true, true, true>;
+    if (avec && bvec) return matvec_tensor_kernel<INNER, true, true, false>;
+    if (avec) return matvec_tensor_kernel<INNER, true, false, false>;
+    if (bvec) return matvec_tensor_kernel<INNER, false, true, false>;
+    return matvec_tensor_kernel<INNER, false, false, false>;
 }
-MatvecFn mv_pick_tensor(int inner, bool avec, bool bvec) {
+MatvecTensorFn mv_pick_tensor(int inner, bool avec, bool bvec, bool tma) {
     switch (inner) {
-        case IN_DIFF_ABS: return mv_pick_tensor_layout<IN_DIFF_ABS>(avec, bvec);
-        case IN_DIFF_SQUARE: return mv_pick_tensor_layout<IN_DIFF_SQUARE>(avec, bvec);
-        case IN_DIFF_POW: return mv_pick_tensor_layout<IN_DIFF_POW>(avec, bvec);
-        case IN_DOT_NOOP: return mv_pick_tensor_layout<IN_DOT_NOOP>(avec, bvec);
+        case IN_DIFF_ABS: return mv_pick_tensor_layout<IN_DIFF_ABS>(avec, bvec, tma);
+        case IN_DIFF_SQUARE: return mv_pick_tensor_layout<IN_DIFF_SQUARE>(avec, bvec, tma);
+        case IN_DIFF_POW: return mv_pick_tensor_layout<IN_DIFF_POW>(avec, bvec, tma);
+        case IN_DOT_NOOP: return mv_pick_tensor_layout<IN_DOT_NOOP>(avec, bvec, tma);
     }
     return nullptr;
 }
@@ -533,6 +603,7 @@ struct MatvecPlan {
     int ot;
     bool avec, bvec;
     bool tensor;              // contraction on the tensor cores (3 x tf32) instead of packed FP32
+    bool tma;                 // tensor kernel with TMA operand staging
     int splits_wanted;
     long long partial_elems;
 };
@@ -584,6 +655,13 @@ int make_matvec_plan(const KmMatvecArgs* a, MatvecPlan* plan) {
     if (p.o_chunks > 65535) return fail(KM_ERR_TOO_LARGE, "too many output channels");
     plan->avec = (p.a_sm == 1) && aligned16(p.A) && (p.a_sk % 4 == 0 || p.K <= 1) && (p.a_sl % 4 == 0);
     plan->bvec = (p.b_sn == 1) && aligned16(p.B) && (p.b_sk % 4 == 0 || p.K <= 1) && (p.b_sl % 4 == 0);
+    // Measured on B200 (K=64, M=N=131072, O=16): TMA staging takes the (b-a)^2 walk from 345 to
+    // 323 ms per 262144^2 pairs; for |b-a| and |b-a|^p it changes nothing (90.9 vs 90.9 ms,
+    // 448 vs 450 ms), so those keep the cp.async pipeline, which accepts every layout.
+    const bool tma_inner = (p.inner_id == IN_DIFF_SQUARE || p.inner_id == IN_DOT_NOOP);
+    plan->tma = plan->tensor && tma_inner && p.K >= 1 && p.M > 0 && p.N > 0 &&
+                tma_operand_ok(p.A, p.a_sm, p.a_sk, p.a_sl, p.K, p.L) &&
+                tma_operand_ok(p.B, p.b_sn, p.b_sk, p.b_sl, p.K, p.L);
 
     // Preferred m split: fill whole waves of 2 blocks per SM when the row tiles alone
     // leave more than ~10 % of a wave idle.
@@ -662,16 +740,32 @@ extern "C" int kermac_b200_kernel_matvec(const KmMatvecArgs* args, void* stream)
         p.y_sn = args->y_stride_n; p.y_so = args->y_stride_o; p.y_sl = args->y_stride_l;
         p.split_stride = 0;
     }
-    MatvecFn fn = plan.tensor ? mv_pick_tensor(p.inner_id, plan.avec, plan.bvec)
-                              : mv_pick(p.inner_id, plan.ot, plan.avec, plan.bvec);
-    if (!fn) return fail(KM_ERR_INTERNAL, "no matvec kernel for inner id %d", p.inner_id);
-    const int smem_bytes = plan.tensor ? MT_SMEM_BYTES : mv_smem_for(plan.ot);
-    if (int rc = cuda_status(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes),
-                             "cudaFuncSetAttribute(matvec_kernel)"))
-        return rc;
     dim3 grid((unsigned)((long long)p.tiles_n * splits), (unsigned)p.o_chunks, (unsigned)p.L);
-    fn<<<grid, MV_THREADS, smem_bytes, st>>>(p);
-    if (int rc = cuda_status(cudaGetLastError(), "launch of matvec_kernel")) return rc;
+    if (plan.tensor) {
+        MatvecTensorFn fn = mv_pick_tensor(p.inner_id, plan.avec, plan.bvec, plan.tma);
+        if (!fn) return fail(KM_ERR_INTERNAL, "no matvec kernel for inner id %d", p.inner_id);
+        if (int rc = cuda_status(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, MT_SMEM_BYTES),
+                                 "cudaFuncSetAttribute(matvec_tensor_kernel)"))
+            return rc;
+        CUtensorMap map_a, map_b;
+        memset(&map_a, 0, sizeof(map_a));
+        memset(&map_b, 0, sizeof(map_b));
+        if (plan.tma) {
+            if (int rc = encode_tma_operand(&map_a, p.A, p.M, p.K, p.L, p.a_sk, p.a_sl, MV_BK)) return rc;
+            if (int rc = encode_tma_operand(&map_b, p.B, p.N, p.K, p.L, p.b_sk, p.b_sl, MV_BK)) return rc;
+        }
+        fn<<<grid, MV_THREADS, MT_SMEM_BYTES, st>>>(p, map_a, map_b);
+        if (int rc = cuda_status(cudaGetLastError(), "launch of matvec_tensor_kernel")) return rc;
+    } else {
+        MatvecFn fn = mv_pick(p.inner_id, plan.ot, plan.avec, plan.bvec);
+        if (!fn) return fail(KM_ERR_INTERNAL, "no matvec kernel for inner id %d", p.inner_id);
+        const int smem_bytes = mv_smem_for(plan.ot);
+        if (int rc = cuda_status(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes),
+                                 "cudaFuncSetAttribute(matvec_kernel)"))
+            return rc;
+        fn<<<grid, MV_THREADS, smem_bytes, st>>>(p);
+        if (int rc = cuda_status(cudaGetLastError(), "launch of matvec_kernel")) return rc;
+    }
     if (splits > 1) {
         const long long total = plan.partial_elems;
         int blocks = (int)(ceil_div_ll(total, 256) < 4LL * sm_count() ? ceil_div_ll(total, 256) : 4LL * sm_count());

@@ -2,6 +2,8 @@
 // tensor-core commits).  Every wait is bounded.
 #pragma once
 
+#include <cuda.h>
+
 #include <cstdint>
 
 namespace km {
@@ -33,4 +35,14 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, int parity) {
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// Tiled TMA copy (no multicast) of one box of a rank-3 tensor into shared memory; the
+// mbarrier receives the byte count.  x is the innermost coordinate: x * 4 bytes must be a
+// multiple of 16.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+
 }  // namespace km

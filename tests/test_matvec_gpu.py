@@ -126,3 +126,19 @@ def test_contraction_argument_is_validated():
     a, b, c = gen((8, 4), 1).cuda(), gen((8, 4), 2).cuda(), gen((2, 8), 3).cuda()
     with pytest.raises(ValueError):
         kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=1.0, contraction="bf16")
+
+
+@pytest.mark.parametrize("shape", [(1028, 260, 20), (132, 128, 1), (516, 4, 33), (4100, 388, 64)])
+def test_m_contiguous_operands(shape):
+    # a[K, M] / b[K, N] storage with 16-byte aligned rows: the TMA-staged variant of the tensor kernel
+    # (partial m / n tiles, partial and single k slabs), batched with a broadcast b
+    M, N, K = shape
+    L, O = 2, 7
+    a, b, c = col_major(gen((L, M, K), 30)), col_major(gen((N, K), 31)), gen((L, O, M), 32)
+    y = kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a.cuda(), b.cuda(), c.cuda(), bandwidth=6.0)
+    ref = ko.kernel_matvec_ref(a, b, c, **LAPLACE_L2, bandwidth=6.0)
+    assert ko.rel_err_signed(y, ref) < TOL
+    y = kermac.kernel_matvec(kermac.kernel_descriptor_mma, a.cuda(), b.cuda(), c.cuda())
+    ref = torch.einsum('lmk,nk,lom->lno', a.double(), b.double(), c.double())
+    assert ko.rel_err_signed(y, ref) < TOL
+    assert _native.device_error_flag() == 0, "a bounded wait inside the kernel ran out"
