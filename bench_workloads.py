@@ -7,6 +7,7 @@ stream, max over ranks.
 """
 from __future__ import annotations
 
+import os
 import time
 
 import torch
@@ -214,13 +215,22 @@ def matvec(args, ctx):
     if ctx.rank == 0:
         lane, mufu = _pipes(_native)
         slab_pairs = float(M) * (stop - start)
-        lane_rate = (2.0 * K + O) * slab_pairs / (k_ms * 1e-3)     # sub + fma per (m,n,k), O fma per (m,n)
+        on_tensor = os.environ.get("KERMAC_B200_CONTRACTION", "auto").lower() != "fp32"
+        # sub + fma per (m, n, k) on the FP32 pipe; the O products per (m, n) run there only with the
+        # FP32 contraction, otherwise on the tensor cores as 3 tf32 products each
+        lane_rate = (2.0 * K + (0 if on_tensor else O)) * slab_pairs / (k_ms * 1e-3)
         line["roofline"] = {"bound": "fp32_simt", "achieved": lane_rate / 1e12, "peak": lane / 1e12,
                             "unit": "T fp32 lane-op/s", "frac": lane_rate / lane,
                             "frac_of_nominal": lane_rate / NOMINAL_LANE_OPS,
                             "peak_source": "measured on this device (fma.rn.f32x2 chains)",
-                            "note": "2*K + O lane-operations per (m, n) pair; 2 MUFU per pair run beside them",
+                            "note": ("2*K lane-operations per (m, n) pair (distance part); the O coefficient products "
+                                     "per pair run on the tcgen05 tensor cores; 2 MUFU per pair run beside them") if on_tensor
+                            else "2*K + O lane-operations per (m, n) pair; 2 MUFU per pair run beside them",
                             "traffic": None}
+        if on_tensor:
+            line["roofline"]["tensor_contraction"] = {
+                "tf32_tflops_issued": 3 * 2.0 * 16 * slab_pairs / (k_ms * 1e-3) / 1e12,
+                "note": "three tf32 MMAs (128 x 16 x 8) per 8 m-columns of every 128-row tile; N = 16 of the MMA is padding above O"}
         if not args.no_cpu:
             rows = 8
             a32, b32 = a_store.t().contiguous(), b_store.t()[:rows].contiguous()
