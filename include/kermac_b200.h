@@ -42,7 +42,7 @@
 extern "C" {
 #endif
 
-#define KERMAC_B200_ABI_VERSION 2
+#define KERMAC_B200_ABI_VERSION 3
 
 /* Rejected preconditions (negative return codes). */
 #define KM_ERR_NULL_POINTER   (-1)
@@ -173,7 +173,10 @@ int kermac_b200_cdist_grad_static(const KmGradArgs* args, void* stream);
  * kermac_b200_build_kernel, but the (m, n) kernel matrix is never stored.
  * c is m-contiguous: c[l][o][m] = c[l * c_stride_l + o * ldc + m].
  * y[l][n][o] = y[l * y_stride_l + n * y_stride_n + o * y_stride_o].
- * The diagonal regularisation rule does not apply here.
+ * The diagonal rule of kermac_b200_build_kernel applies to the kernel-matrix values
+ * before the product (only with a kernel function): where reg_off_x + m == reg_off_y + n
+ * and regularization != 0 the value is 1 + regularization, which gives
+ * y = (K + lambda I) c for a square K(X, X) without a second pass.
  *
  * contraction selects where the coefficient product runs: KM_CONTRACT_TENSOR (and
  * KM_CONTRACT_AUTO) on the tcgen05 tensor cores as three tf32 products per term
@@ -196,6 +199,8 @@ typedef struct KmMatvecArgs {
     void*   scratch; int64_t scratch_bytes;
     int32_t split_m;          /* 0 = automatic (1 when scratch is NULL) */
     int32_t contraction;      /* KM_CONTRACT_* */
+    KmHyper regularization;
+    int32_t reg_off_x, reg_off_y;
 } KmMatvecArgs;
 
 int kermac_b200_kernel_matvec(const KmMatvecArgs* args, void* stream);

@@ -11,7 +11,7 @@ import os
 import threading
 from typing import Optional
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 # enum values of include/kermac_b200.h
 INNER_DIFF, INNER_DOT = 0, 1
@@ -85,6 +85,8 @@ class KmMatvecArgs(C.Structure):
         ("scratch", C.c_void_p), ("scratch_bytes", C.c_int64),
         ("split_m", C.c_int32),
         ("contraction", C.c_int32),
+        ("regularization", KmHyper),
+        ("reg_off_x", C.c_int32), ("reg_off_y", C.c_int32),
     ]
 
 

@@ -39,7 +39,8 @@ struct MatvecParams {
     const float* C; long long ldc, c_sl;
     float*       Y; long long y_sn, y_so, y_sl;     // destination (y, or scratch when split)
     int inner_id, outer_power, kernel_type;
-    KmHyper p_inner, p_outer, bandwidth;
+    KmHyper p_inner, p_outer, bandwidth, regularization;
+    int   reg_off_m, reg_off_n;                       // diagonal rule: reg_off_m + m == reg_off_n + n
     float epsilon;
     int tiles_n, splits, o_chunks;
     int m_per_split;                                  // multiple of MV_TILE
@@ -150,6 +151,18 @@ __global__ void __launch_bounds__(MV_THREADS, 2) matvec_kernel(const __grid_cons
                 const int mm = idx & (MV_TILE - 1), o = idx >> 7;
                 const bool ok = (mc0 + mm < m_end) && (o0 + o < p.O);
                 s_c[mm * OT + o] = ok ? C[(long long)(o0 + o) * p.ldc + mc0 + mm] : 0.0f;
+            }
+            {
+                // Diagonal rule, applied to the parked tile: row n holds 1 + reg at m = n + delta.
+                // Read once per tile, so nothing of it stays live through the k loop.
+                const float reg       = (p.kernel_type != KM_KERNEL_NONE) ? read_hyper(p.regularization, l) : 0.0f;
+                const long long delta = (long long)p.reg_off_n - (long long)p.reg_off_m;
+                if (reg != 0.0f && mc0 + MV_TILE > n0 + delta && mc0 < n0 + delta + MV_TILE) {
+                    __syncthreads();
+                    const long long m_want = n0 + cn + delta;
+                    if (ch == 0 && m_want >= mc0 && m_want < mc0 + MV_TILE && m_want < m_end)
+                        s_kt[cn * MV_KT_PITCH + (int)(m_want - mc0)] = 1.0f + reg;
+                }
             }
             __syncthreads();
             if constexpr (OT >= 4) {
@@ -415,6 +428,10 @@ matvec_tensor_kernel(const __grid_constant__ MatvecParams p, const __grid_consta
         if (kt == ktiles - 1) {
             const int mc0 = m_begin + chunk * MV_TILE;
             const uint32_t d_set = tmem + (chunk & 1) * MT_TMEM_SET;
+            // diagonal rule; read here, once per tile, so nothing of it stays live through the k loop
+            const float reg       = (p.kernel_type != KM_KERNEL_NONE) ? read_hyper(p.regularization, l) : 0.0f;
+            const long long delta = (long long)p.reg_off_n - (long long)p.reg_off_m;   // diagonal: m == n + delta
+            const bool on_diagonal = (reg != 0.0f && mc0 + MV_TILE > n0 + delta && mc0 < n0 + delta + MV_TILE);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 // outer chain of this round's 32 values, in place; in the last, partial tile of the m
@@ -466,6 +483,20 @@ matvec_tensor_kernel(const __grid_constant__ MatvecParams p, const __grid_consta
                     const int off = (cq >> 3) * MT_SLAB_B + co * 128 + (((cq & 7) ^ (co & 7)) << 4);
                     *reinterpret_cast<float4*>(tiles + MT_OFF_B_HI + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
                     *reinterpret_cast<float4*>(tiles + MT_OFF_B_LO + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+                }
+                if (on_diagonal) {
+                    // diagonal rule on the parked tile: row n holds 1 + reg at m = n + delta
+                    __syncthreads();
+                    const long long m_want = n0 + cn + delta;
+                    const int ml           = (int)(m_want - mc0);          // column inside the 128-wide tile
+                    if (ch == 0 && m_want >= mc0 && ml < MV_TILE && m_want < m_end && ((ml >> 5) & 1) == h) {
+                        const int q     = (ml >> 6) * 32 + (ml & 31);      // column inside this round
+                        const int off   = (q >> 5) * MT_SLAB_A + cn * 128 + ((((q & 31) >> 2) ^ (cn & 7)) << 4) + (q & 3) * 4;
+                        const float one = 1.0f + reg;
+                        const float hi  = tf32_hi(one);
+                        *reinterpret_cast<float*>(tiles + MT_OFF_A_HI + off) = hi;
+                        *reinterpret_cast<float*>(tiles + MT_OFF_A_LO + off) = one - hi;
+                    }
                 }
                 tc::fence_smem_to_async();
                 tc::fence_before_sync();
@@ -627,7 +658,7 @@ int make_matvec_plan(const KmMatvecArgs* a, MatvecPlan* plan) {
     if (a->a_stride_l < 0 || a->b_stride_l < 0 || a->c_stride_l < 0 || a->y_stride_l < 0 || a->y_stride_n < 0 ||
         a->y_stride_o < 0)
         return fail(KM_ERR_BAD_STRIDE, "strides must be non-negative");
-    if (!hyper_ok(a->p_inner) || !hyper_ok(a->p_outer) || !hyper_ok(a->bandwidth))
+    if (!hyper_ok(a->p_inner) || !hyper_ok(a->p_outer) || !hyper_ok(a->bandwidth) || !hyper_ok(a->regularization))
         return fail(KM_ERR_BAD_HYPERPARAM, "hyper-parameter vectors need a non-negative batch stride");
     if (a->split_m < 0) return fail(KM_ERR_BAD_SHAPE, "split_m must be >= 0");
     if (a->contraction < KM_CONTRACT_AUTO || a->contraction > KM_CONTRACT_TENSOR)
@@ -644,6 +675,8 @@ int make_matvec_plan(const KmMatvecArgs* a, MatvecPlan* plan) {
     p.outer_power = a->outer_power;
     p.kernel_type = a->kernel_type;
     p.p_inner = a->p_inner; p.p_outer = a->p_outer; p.bandwidth = a->bandwidth;
+    p.regularization = a->regularization;
+    p.reg_off_m = a->reg_off_x; p.reg_off_n = a->reg_off_y;
     p.epsilon = a->epsilon;
     plan->tensor = (a->contraction != KM_CONTRACT_FP32);
     int ot = 2;

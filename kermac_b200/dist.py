@@ -286,7 +286,11 @@ def kernel_matvec_sharded(kernel_descriptor, a: torch.Tensor, b: torch.Tensor, c
         from .matvec import kernel_matvec as _matvec
 
         def compute(a_, b_, c_, out):
-            return _matvec(kernel_descriptor, a_, b_, c_, out=out, **hyper)
+            # the slab's row 0 is row `start` of the whole problem: move the diagonal with it
+            kw = dict(hyper)
+            if kw.get("regularization") is not None:
+                kw["regularization_offset_y"] = int(kw.get("regularization_offset_y", 0)) + start
+            return _matvec(kernel_descriptor, a_, b_, c_, out=out, **kw)
     if stop > start:
         compute(a, b[start:stop], c, slab)
     if buf is None:

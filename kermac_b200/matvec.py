@@ -21,8 +21,9 @@ from .common import merge_batch_size, tensor_stats
 __all__ = ["kernel_matvec"]
 
 
-def _marshal_matvec(kernel_descriptor, a, b, c, out, p, inner_p, outer_p, bandwidth, epsilon):
-    _check_descriptor_arguments(kernel_descriptor, p, inner_p, outer_p, bandwidth, epsilon, None)
+def _marshal_matvec(kernel_descriptor, a, b, c, out, p, inner_p, outer_p, bandwidth, epsilon, regularization=None,
+                    regularization_offset_x=0, regularization_offset_y=0):
+    _check_descriptor_arguments(kernel_descriptor, p, inner_p, outer_p, bandwidth, epsilon, regularization)
     for name, t in (('a', a), ('b', b), ('c', c)):
         if not isinstance(t, torch.Tensor):
             raise TypeError(f"{name} must be a PyTorch tensor")
@@ -43,7 +44,7 @@ def _marshal_matvec(kernel_descriptor, a, b, c, out, p, inner_p, outer_p, bandwi
     L = 1
     for name, value, dims, optional in (
             ('p', p, 0, True), ('inner_p', inner_p, 0, True), ('outer_p', outer_p, 0, True),
-            ('bandwidth', bandwidth, 0, True),
+            ('bandwidth', bandwidth, 0, True), ('regularization', regularization, 0, True),
             ('a', a, 2, False), ('b', b, 2, False), ('c', c, 2, False), ('out', out, 2, True)):
         L = merge_batch_size(name, L, value, expected_dims=dims, can_be_none=optional)
 
@@ -66,7 +67,8 @@ def _marshal_matvec(kernel_descriptor, a, b, c, out, p, inner_p, outer_p, bandwi
     else:
         out = torch.empty((L, N, O), dtype=torch.float32, device=a.device)
 
-    for name, value in (('inner_p', inner_p), ('outer_p', outer_p), ('p', p), ('bandwidth', bandwidth)):
+    for name, value in (('inner_p', inner_p), ('outer_p', outer_p), ('p', p), ('bandwidth', bandwidth),
+                        ('regularization', regularization)):
         _check_hyper_tensor(name, value, a.device)
     inner_p, outer_p = _resolve_powers(p, inner_p, outer_p)
 
@@ -89,8 +91,11 @@ def _marshal_matvec(kernel_descriptor, a, b, c, out, p, inner_p, outer_p, bandwi
     args.p_outer = _native.hyper(outer_p)
     args.bandwidth = _native.hyper(bandwidth)
     args.epsilon = 1e-5 if epsilon is None else float(epsilon)
+    args.regularization = _native.hyper(regularization)
+    args.reg_off_x = int(regularization_offset_x)
+    args.reg_off_y = int(regularization_offset_y)
     args.scratch, args.scratch_bytes, args.split_m = None, 0, 0
-    return args, out, (inner_p, outer_p, bandwidth)
+    return args, out, (inner_p, outer_p, bandwidth, regularization)
 
 
 _CONTRACTIONS = {"auto": 0, "fp32": 1, "tensor": 2}
@@ -116,6 +121,9 @@ def kernel_matvec(
     outer_p: Optional[Union[float, torch.Tensor]] = None,
     bandwidth: Optional[Union[float, torch.Tensor]] = None,
     epsilon: Optional[float] = None,
+    regularization: Optional[Union[float, torch.Tensor]] = None,
+    regularization_offset_x: int = 0,
+    regularization_offset_y: int = 0,
     split_m: int = 0,
     contraction: Optional[str] = None,
     debug=False,
@@ -124,14 +132,17 @@ def kernel_matvec(
 
     a: (M, K) / (L, M, K); b: (N, K) / (L, N, K); c: (O, M) / (L, O, M) with stride 1 along
     m; out: (N, O) / (L, N, O), allocated as (L, N, O) when None.  Hyper-parameters as in
-    `run_kernel`, without the diagonal regularisation.  `split_m` > 1 divides the sum over m
+    `run_kernel`, including the diagonal rule: where regularization_offset_x + m ==
+    regularization_offset_y + n the kernel value is 1 + regularization, so a square K(X, X)
+    gives (K + lambda I) c in one pass.  `split_m` > 1 divides the sum over m
     among that many thread blocks per row tile (0 picks automatically); partial sums are
     added in a fixed order, so the result does not depend on scheduling.  `contraction`
     selects where the coefficient product runs: "tensor" (tcgen05 tensor cores, three tf32
     products per term, fp32-level accuracy), "fp32" (packed FP32 FMAs) or "auto" / None
     (the environment variable KERMAC_B200_CONTRACTION, else the library default: tensor).
     """
-    args, out, keep_alive = _marshal_matvec(kernel_descriptor, a, b, c, out, p, inner_p, outer_p, bandwidth, epsilon)
+    args, out, keep_alive = _marshal_matvec(kernel_descriptor, a, b, c, out, p, inner_p, outer_p, bandwidth, epsilon,
+                                            regularization, regularization_offset_x, regularization_offset_y)
     stream_ptr = _current_stream_for(a.device)
     args.split_m = int(split_m)
     args.contraction = _contraction_code(contraction)

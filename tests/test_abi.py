@@ -37,7 +37,7 @@ def test_struct_sizes_match_the_header_layout():
     assert ctypes.sizeof(_native.KmHyper) == 24
     assert ctypes.sizeof(_native.KmBuildArgs) == 16 + 3 * 32 + 16 + 4 * 24 + 16 + 8
     assert ctypes.sizeof(_native.KmGradArgs) == 24 + 4 * 24 + 32 + 8 + 24 + 16 + 8
-    assert ctypes.sizeof(_native.KmMatvecArgs) == 24 + 2 * 32 + 24 + 32 + 16 + 3 * 24 + 8 + 16 + 8
+    assert ctypes.sizeof(_native.KmMatvecArgs) == 24 + 2 * 32 + 24 + 32 + 16 + 3 * 24 + 8 + 16 + 8 + 24 + 8
 
 
 def _build_args(**kw):

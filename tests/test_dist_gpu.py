@@ -46,6 +46,12 @@ def _worker(rank, world, port, results):
         y = kdist.kernel_matvec_sharded(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=8.0)
         y1 = kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=8.0)[0]
         ok = ok and torch.equal(y, y1)
+        # the diagonal rule follows the rows into the shards (the diagonal crosses the second rank's slab)
+        y = kdist.kernel_matvec_sharded(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=8.0,
+                                        regularization=0.25, regularization_offset_x=300)
+        y1 = kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=8.0,
+                                  regularization=0.25, regularization_offset_x=300)[0]
+        ok = ok and torch.equal(y, y1)
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()

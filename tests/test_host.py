@@ -252,3 +252,16 @@ def test_kernel_matvec_marshalling(recorder, monkeypatch):
         kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a, b, torch.zeros(3, 8), bandwidth=8.0)
     with pytest.raises(ValueError, match="'bandwidth' is not set"):
         kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a, b, c)
+    # contraction mode, diagonal rule
+    assert args.contraction == 0 and args.regularization.value == 0.0
+    monkeypatch.setenv("KERMAC_B200_CONTRACTION", "fp32")
+    kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=8.0, regularization=0.5,
+                         regularization_offset_x=3, regularization_offset_y=-2)
+    args = recorder[-1][1]
+    assert args.contraction == 1 and args.regularization.value == 0.5 and (args.reg_off_x, args.reg_off_y) == (3, -2)
+    kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=8.0, contraction="tensor")
+    assert recorder[-1][1].contraction == 2
+    with pytest.raises(ValueError, match="contraction must be one of"):
+        kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=8.0, contraction="bf16")
+    with pytest.raises(ValueError, match="'KernelType' is 'None'"):
+        kermac.kernel_matvec(kermac.kernel_descriptor_l2_norm, a, b, c, regularization=0.1)

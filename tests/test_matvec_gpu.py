@@ -142,3 +142,27 @@ def test_m_contiguous_operands(shape):
     ref = torch.einsum('lmk,nk,lom->lno', a.double(), b.double(), c.double())
     assert ko.rel_err_signed(y, ref) < TOL
     assert _native.device_error_flag() == 0, "a bounded wait inside the kernel ran out"
+
+
+@pytest.mark.parametrize("layout", ["row", "col"])
+def test_diagonal_rule_gives_regularised_product(layout):
+    # square K(X, X): the diagonal becomes 1 + lambda, so y = (K + lambda I) c since K(x, x) = 1
+    M, K, O, lam = 900, 24, 5, 0.37
+    x, c = gen((M, K), 40), gen((O, M), 41)
+    xd = (col_major(x) if layout == "col" else x).cuda()
+    y = kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, xd, xd, c.cuda(), bandwidth=4.0, regularization=lam)
+    ref = ko.kernel_matvec_ref(x, x, c, **LAPLACE_L2, bandwidth=4.0, regularization=lam)
+    assert ko.rel_err_signed(y, ref) < TOL
+    plain = ko.kernel_matvec_ref(x, x, c, **LAPLACE_L2, bandwidth=4.0)
+    assert ko.rel_err_signed(ref, plain + lam * c.t().double().unsqueeze(0)) < 1e-7     # lambda is rounded to fp32
+    # shifted diagonal, rectangular operands, split over m, per-batch lambda
+    L, N = 2, 300
+    a, b, cc = gen((L, M, K), 42), gen((N, K), 43), gen((L, O, M), 44)
+    lam_t = torch.tensor([0.5, -0.25])
+    for split in (0, 3):
+        y = kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l1, a.cuda(), b.cuda(), cc.cuda(), bandwidth=9.0,
+                                 regularization=lam_t.cuda(), regularization_offset_x=-200, regularization_offset_y=57,
+                                 split_m=split)
+        ref = ko.kernel_matvec_ref(a, b, cc, inner_operator="DIFF", inner_power="ABS", outer_power="NOOP",
+                                   kernel_type="LAPLACE", bandwidth=9.0, regularization=lam_t, reg_off_x=-200, reg_off_y=57)
+        assert ko.rel_err_signed(y, ref) < TOL
