@@ -42,7 +42,7 @@
 extern "C" {
 #endif
 
-#define KERMAC_B200_ABI_VERSION 3
+#define KERMAC_B200_ABI_VERSION 4
 
 /* Rejected preconditions (negative return codes). */
 #define KM_ERR_NULL_POINTER   (-1)
@@ -107,7 +107,16 @@ typedef struct KmBuildArgs {
                                  buffer (e.g. torch symmetric memory's multicast_ptr): results are written with
                                  multimem.st, so each GPU's buffer receives them while the kernel computes.  The
                                  caller synchronises the GPUs afterwards.  No reference counterpart. */
+    int32_t symmetry;         /* KM_SYMMETRY_AUTO: when a and b are the same matrix (same pointer, strides and
+                                 extent), reg_off_x == reg_off_y and the chain is even in the difference (|.|,
+                                 square, |.|^p, or any product), only the tiles on and above the diagonal are
+                                 computed and each is also written transposed: half the arithmetic, bit-identical
+                                 results (equal to rounding for |.|^p, whose exp2 takes one of two routes).  KM_SYMMETRY_OFF computes every tile.  The reference declares a Symmetry
+                                 enum (src/kermac/build_a_kernel.py:35-37) that nothing uses. */
 } KmBuildArgs;
+
+#define KM_SYMMETRY_AUTO 0
+#define KM_SYMMETRY_OFF  1
 
 /* Kernel variants of kermac_b200_build_kernel (for benchmarks and tests). */
 #define KM_VARIANT_AUTO     0

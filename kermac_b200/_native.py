@@ -11,7 +11,7 @@ import os
 import threading
 from typing import Optional
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 # enum values of include/kermac_b200.h
 INNER_DIFF, INNER_DOT = 0, 1
@@ -53,6 +53,7 @@ class KmBuildArgs(C.Structure):
         ("epsilon", C.c_float),
         ("variant", C.c_int32),
         ("out_multicast", C.c_int32),
+        ("symmetry", C.c_int32),
     ]
 
 

@@ -274,6 +274,9 @@ def _marshal_build(kernel_descriptor, a, b, out, p, inner_p, outer_p, bandwidth,
     args.reg_off_y = int(regularization_offset_y)
     args.epsilon = 1e-5 if epsilon is None else float(epsilon)
     args.variant = _forced_variant()
+    # symmetric problems (a and b the same view) are computed from one triangle of tiles and
+    # mirrored, with identical bits; KERMAC_B200_SYMMETRY=off computes every tile
+    args.symmetry = 1 if os.environ.get("KERMAC_B200_SYMMETRY", "auto").strip().lower() == "off" else 0
     keep_alive = (inner_p, outer_p, bandwidth, regularization)
     return args, out, keep_alive
 

@@ -72,16 +72,23 @@ __device__ __forceinline__ void stage_operand(float* dst, const float* base, lon
 // Applies the outer chain to one thread's 8 x 8 block and stores it.
 // Coordinates: acc[j][mp] holds rows n = n_base + (j / 4) * 16 + (j % 4) and
 // columns m = m_base + (mp / 2) * 32 + (mp % 2) * 2 + {0, 1}.
-template <int INNER>
-__device__ __forceinline__ void finish_block(const BuildParams& p, int l, u64 (&acc)[8][4], int m_base, int n_base) {
+// With `mirror` the block is also written transposed, to C[m][n]: the kernel matrix of
+// a symmetric problem, of which only the tiles on and above the diagonal are computed.
+// MIRROR = false compiles the transposed stores out, so kernels of ordinary problems carry none of it.
+template <int INNER, bool MIRROR>
+__device__ __forceinline__ void finish_block(const BuildParams& p, int l, u64 (&acc)[8][4], int m_base, int n_base,
+                                             bool mirror) {
     const Epilogue epi = make_epilogue(p.outer_power, p.kernel_type, p.p_outer, p.bandwidth, p.epsilon, l);
     float reg = 0.0f;
     if (p.kernel_type != KM_KERNEL_NONE) reg = read_hyper(p.regularization, l);
     float* C = p.C + static_cast<long long>(l) * p.c_sl;
+    const bool mc = p.c_multicast != 0;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const int n = n_base + (j >> 2) * 16 + (j & 3);
-        if (n >= p.N) continue;
+        if constexpr (!MIRROR) {
+            if (n >= p.N) continue;
+        }
         float* row = C + static_cast<long long>(n) * p.c_ld;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -97,18 +104,54 @@ __device__ __forceinline__ void finish_block(const BuildParams& p, int l, u64 (&
                 if (reg != 0.0f && (p.reg_off_m + m + e == p.reg_off_n + n)) x = 1.0f + reg;
                 v[e] = x;
             }
+            if constexpr (MIRROR) {
+                acc[j][2 * h]     = pack2(v[0], v[1]);     // kept for the mirror image
+                acc[j][2 * h + 1] = pack2(v[2], v[3]);
+            }
+            if (n >= p.N) continue;
             if (p.c_vec4 && m + 3 < p.M) {
-                store_result4(row + m, v[0], v[1], v[2], v[3], p.c_multicast != 0);
+                store_result4(row + m, v[0], v[1], v[2], v[3], mc);
             } else {
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                    if (m + e < p.M) store_result1(row + m + e, v[e], p.c_multicast != 0);
+                    if (m + e < p.M) store_result1(row + m + e, v[e], mc);
+            }
+        }
+    }
+    if constexpr (!MIRROR) return;
+    if (!mirror) return;
+    // C[m][n]: for each of the thread's 8 columns m, its rows n come in two runs of four
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int m = m_base + (i >> 1) * 32 + (i & 1) * 2 + half;
+            if (m >= p.M) continue;
+            float* row = C + static_cast<long long>(m) * p.c_ld;
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+                const int n = n_base + g * 16;
+                float v[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float lo, hi;
+                    unpack2(acc[g * 4 + e][i], lo, hi);
+                    v[e] = half ? hi : lo;
+                }
+                if (p.c_vec4 && n + 3 < p.N) {
+                    store_result4(row + n, v[0], v[1], v[2], v[3], mc);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (n + e < p.N) store_result1(row + n + e, v[e], mc);
+                }
             }
         }
     }
 }
 
-template <int INNER, bool AVEC, bool BVEC>
+// SYM: a and b are the same matrix and the chain is symmetric in (m, n); see BuildParams::symmetric.
+template <int INNER, bool AVEC, bool BVEC, bool SYM>
 __global__ void __launch_bounds__(CPA_THREADS, 2) build_cpasync_kernel(const __grid_constant__ BuildParams p) {
     extern __shared__ __align__(16) float smem[];
     const int tid  = threadIdx.x;
@@ -118,6 +161,7 @@ __global__ void __launch_bounds__(CPA_THREADS, 2) build_cpasync_kernel(const __g
 
     int tm, tn;
     tile_coords(blockIdx.x, p.tiles_m, p.tiles_n, p.panel, tm, tn);
+    if (SYM && tn < tm) return;   // the tile's mirror image (tn, tm) writes this part of C
     const int m0 = tm * CPA_TILE;
     const int n0 = tn * CPA_TILE;
 
@@ -170,7 +214,7 @@ __global__ void __launch_bounds__(CPA_THREADS, 2) build_cpasync_kernel(const __g
     }
     cp_async_wait<0>();
 
-    finish_block<INNER>(p, l, acc, m0 + tm_off, n0 + tn_off);
+    finish_block<INNER, SYM>(p, l, acc, m0 + tm_off, n0 + tn_off, SYM && tm != tn);
 }
 
 }  // namespace km

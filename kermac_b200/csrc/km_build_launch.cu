@@ -11,8 +11,9 @@ namespace km {
 
 namespace {
 
-BuildKernelFn cpasync_kernel(int inner, bool avec, bool bvec) {
-    return inner < IN_DOT_NOOP ? cpasync_kernel_diff(inner, avec, bvec) : cpasync_kernel_dot(inner, avec, bvec);
+BuildKernelFn cpasync_kernel(int inner, bool avec, bool bvec, bool symmetric) {
+    return inner < IN_DOT_NOOP ? cpasync_kernel_diff(inner, avec, bvec, symmetric)
+                               : cpasync_kernel_dot(inner, avec, bvec, symmetric);
 }
 
 // One of the two layouts TensorStats accepts (src/kermac/common.py:96-102):
@@ -107,6 +108,18 @@ int make_plan(const KmBuildArgs* a, BuildPlan* plan) {
         return fail(KM_ERR_BAD_ENUM, "out_multicast must be 0 or 1");
     p.c_multicast = a->out_multicast;
 
+    // a and b the same matrix, a chain that does not change when m and n trade places (the
+    // diagonal rule included): compute the tiles on and above the diagonal and mirror them.
+    // The mirrored values are the same bits the skipped tiles would have produced: the sum
+    // over k runs in the same order over the same terms.
+    if (a->symmetry < KM_SYMMETRY_AUTO || a->symmetry > KM_SYMMETRY_OFF)
+        return fail(KM_ERR_BAD_ENUM, "symmetry must be KM_SYMMETRY_AUTO or KM_SYMMETRY_OFF");
+    const bool even_chain = (p.inner_id == IN_DIFF_ABS || p.inner_id == IN_DIFF_SQUARE || p.inner_id == IN_DIFF_POW ||
+                             p.inner_id >= IN_DOT_NOOP);
+    p.symmetric = (a->symmetry == KM_SYMMETRY_AUTO) && even_chain && p.M == p.N && p.tiles_m > 1 && p.A == p.B &&
+                  p.a_sm == p.b_sn && p.a_sk == p.b_sk && p.a_sl == p.b_sl && p.reg_off_m == p.reg_off_n &&
+                  !p.c_multicast;
+
     plan->avec = (p.a_sm == 1) && aligned16(p.A) && (p.a_sk % 4 == 0 || p.K <= 1) && (p.a_sl % 4 == 0);
     plan->bvec = (p.b_sn == 1) && aligned16(p.B) && (p.b_sk % 4 == 0 || p.K <= 1) && (p.b_sl % 4 == 0);
 
@@ -136,7 +149,7 @@ extern "C" int kermac_b200_build_kernel(const KmBuildArgs* args, void* stream) {
 
     if (plan.variant == KM_VARIANT_TMA) return launch_build_tma(p, st);
 
-    BuildKernelFn fn = cpasync_kernel(p.inner_id, plan.avec, plan.bvec);
+    BuildKernelFn fn = cpasync_kernel(p.inner_id, plan.avec, plan.bvec, p.symmetric != 0);
     if (!fn) return fail(KM_ERR_INTERNAL, "no kernel for inner id %d", p.inner_id);
     if (int rc = cuda_status(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, BUILD_CPA_SMEM_BYTES),
                              "cudaFuncSetAttribute(build_cpasync_kernel)"))
@@ -167,8 +180,8 @@ extern "C" int kermac_b200_describe_variant(const KmBuildArgs* args, char* buf, 
     const BuildParams& p = plan.p;
     snprintf(buf, (size_t)buf_len,
              "build_kernel variant=%s inner=%s outer_power=%d kernel_type=%d exchanged=%d a_vec16=%d b_vec16=%d "
-             "out_vec16=%d tiles=%dx%d batches=%d",
+             "out_vec16=%d tiles=%dx%d batches=%d symmetric=%d",
              plan.variant == KM_VARIANT_TMA ? "tma" : "cpasync", kInnerNames[p.inner_id], p.outer_power, p.kernel_type,
-             plan.swapped ? 1 : 0, plan.avec ? 1 : 0, plan.bvec ? 1 : 0, p.c_vec4, p.tiles_m, p.tiles_n, p.L);
+             plan.swapped ? 1 : 0, plan.avec ? 1 : 0, plan.bvec ? 1 : 0, p.c_vec4, p.tiles_m, p.tiles_n, p.L, p.symmetric);
     return 0;
 }

@@ -33,6 +33,8 @@ struct BuildParams {
     int   panel;                    // rasterisation: n-tiles per panel
     int   c_vec4;                   // C rows may be written with 16-byte stores
     int   c_multicast;              // C is an NVSwitch multicast address: write with multimem.st
+    int   symmetric;                // A and B are the same matrix and the chain is symmetric in (m, n):
+                                    // tiles with tile_n < tile_m are skipped, the others also write their mirror image
 };
 
 // Maps a linear tile index to (tile_m, tile_n) so that thread blocks that run at

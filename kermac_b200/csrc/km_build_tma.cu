@@ -36,7 +36,7 @@ constexpr int TMA_TILE    = 128;
 constexpr int TMA_THREADS = 256;
 constexpr int TMA_WARPS   = TMA_THREADS / 32;
 
-template <int INNER, int BK, int STAGES, int LAG>
+template <int INNER, int BK, int STAGES, int LAG, bool SYM>
 __global__ void __launch_bounds__(TMA_THREADS, 2)
 build_tma_kernel(const __grid_constant__ BuildParams p, const __grid_constant__ CUtensorMap map_a,
                  const __grid_constant__ CUtensorMap map_b) {
@@ -59,6 +59,7 @@ build_tma_kernel(const __grid_constant__ BuildParams p, const __grid_constant__ 
 
     int tm, tn;
     tile_coords(blockIdx.x, p.tiles_m, p.tiles_n, p.panel, tm, tn);
+    if (SYM && tn < tm) return;   // the tile's mirror image (tn, tm) writes this part of C
     const int m0 = tm * TMA_TILE;
     const int n0 = tn * TMA_TILE;
     const int K  = p.K;
@@ -137,7 +138,7 @@ build_tma_kernel(const __grid_constant__ BuildParams p, const __grid_constant__ 
         }
         return;
     }
-    finish_block<INNER>(p, l, acc, m0 + tm_off, n0 + tn_off);
+    finish_block<INNER, SYM>(p, l, acc, m0 + tm_off, n0 + tn_off, SYM && tm != tn);
 }
 
 // ------------------------------------------------------------------ host side
@@ -204,14 +205,15 @@ struct TmaShape {
 };
 
 struct TmaChoice {
-    TmaKernelFn fn;
+    TmaKernelFn fn, fn_symmetric;
     int bk, smem;
 };
 
 template <int INNER>
 TmaChoice tma_choice() {
     typedef TmaShape<INNER> S;
-    return {build_tma_kernel<INNER, S::BK, S::STAGES, S::LAG>, S::BK, S::SMEM};
+    return {build_tma_kernel<INNER, S::BK, S::STAGES, S::LAG, false>, build_tma_kernel<INNER, S::BK, S::STAGES, S::LAG, true>,
+            S::BK, S::SMEM};
 }
 
 TmaChoice tma_kernel(int inner) {
@@ -221,7 +223,7 @@ TmaChoice tma_kernel(int inner) {
         case IN_DIFF_POW: return tma_choice<IN_DIFF_POW>();
         case IN_DOT_NOOP: return tma_choice<IN_DOT_NOOP>();
     }
-    return {nullptr, 0, 0};
+    return {nullptr, nullptr, 0, 0};
 }
 
 }  // namespace
@@ -249,7 +251,7 @@ bool tma_preferred(const BuildParams& p) {
 
 int launch_build_tma(const BuildParams& p, cudaStream_t stream) {
     const TmaChoice choice = tma_kernel(p.inner_id);
-    TmaKernelFn fn         = choice.fn;
+    TmaKernelFn fn         = p.symmetric ? choice.fn_symmetric : choice.fn;
     if (!fn) return fail(KM_ERR_INTERNAL, "no TMA kernel for inner id %d", p.inner_id);
     const int kBK = choice.bk, kSmemBytes = choice.smem;
     if (int rc = cuda_status(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),

@@ -17,7 +17,7 @@ import torch
 import torch.distributed as dist_
 
 __all__ = ["shard_rows", "slab_sizes", "gather_buffer", "gather_rows_inplace", "gather_rows", "cdist_sharded",
-           "OverlappedCdist", "kernel_matvec_sharded"]
+           "OverlappedCdist", "kernel_matvec_sharded", "cdist_grad_sharded"]
 
 
 ROW_ALIGN = 128   # slab boundaries fall on output-tile boundaries (and keep slices 16-byte aligned)
@@ -296,3 +296,48 @@ def kernel_matvec_sharded(kernel_descriptor, a: torch.Tensor, b: torch.Tensor, c
     if buf is None:
         return slab
     return gather_rows_inplace(buf, n_total, group)
+
+
+GRAD_ROW_ALIGN = 16   # the gradient kernels tile n in multiples of 16
+
+
+def cdist_grad_sharded(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, d: torch.Tensor, p=2.0,
+                       group=None, gather: bool = True, compute: Optional[Callable] = None) -> torch.Tensor:
+    """`cdist_grad` sharded over the rows n of `b` (N, K) and `d` (N, M) for 2-D operands.
+
+    Every output slice out[:, n, :] depends on row n of `b` and `d` only, so rank r computes
+    out[:, rows_r, :] from all of `a` (K, M) and `c` (O, K) with no exchange; the contracted
+    dimension k is never split across ranks (that would need an all-reduce).  Returns the full
+    (O, N, M) tensor when `gather` (one all-gather of the slabs, then a concatenation along n),
+    else this rank's (O, rows_r, M) slab.  `compute(a, b_rows, c, d_rows, out=...)` defaults to
+    `kermac_b200.cdist_grad`.
+    """
+    if a.dim() != 2 or b.dim() != 2 or c.dim() != 2 or d.dim() != 2:
+        raise ValueError("cdist_grad_sharded takes 2-D a, b, c and d")
+    world = dist_.get_world_size(group) if dist_.is_initialized() else 1
+    rank = dist_.get_rank(group) if dist_.is_initialized() else 0
+    n_total, m_total, o_total = b.size(0), a.size(1), c.size(0)
+    if d.size(0) != n_total:
+        raise ValueError(f"d must have {n_total} rows like b, got {d.size(0)}")
+    sizes = slab_sizes(n_total, world, GRAD_ROW_ALIGN)
+    start = sum(sizes[:rank])
+    stop = start + sizes[rank]
+    largest = max(sizes) if sizes else 0
+    if compute is None:
+        from .cdist_grad import cdist_grad as _grad
+
+        def compute(a_, b_, c_, d_, out):
+            return _grad(a_, b_, c_, d_, out=out, p=p)
+    if gather and world > 1:
+        buf = torch.empty((world, o_total, largest, m_total), dtype=torch.float32, device=a.device)
+        slab = buf[rank, :, :sizes[rank]]
+    else:
+        buf, slab = None, torch.empty((o_total, stop - start, m_total), dtype=torch.float32, device=a.device)
+    if stop > start:
+        compute(a, b[start:stop], c, d[start:stop], slab)
+    if buf is None:
+        return slab
+    flat = buf.view(world * o_total, largest, m_total)       # concatenation along dim 0, as the collective expects
+    dist_.all_gather_into_tensor(flat, flat[rank * o_total:(rank + 1) * o_total], group=group)
+    return torch.cat([buf[r, :, :sizes[r]] for r in range(world) if sizes[r] > 0], dim=1)
+

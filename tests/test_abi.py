@@ -100,6 +100,20 @@ def test_describe_variant_reports_the_plan():
     col = _build_args(m=256, n=256, k=64, a_stride_m=1, a_stride_k=256, b_stride_n=1, b_stride_k=256, out_stride_n=256,
                       inner_power=_native.POW_SQUARE, outer_power=_native.POW_SQRT)
     assert "variant=tma" in _native.describe_build(col)
+    # a and b are the same matrix here and the square is even in the difference: one triangle of tiles
+    assert "symmetric=1" in _native.describe_build(col) and "symmetric=0" in text
+    col.symmetry = 1
+    assert "symmetric=0" in _native.describe_build(col)
+    col.symmetry = 0
+    col.reg_off_x = 1
+    assert "symmetric=0" in _native.describe_build(col)
+    col.reg_off_x = 0
+    col.b = 0x2000
+    assert "symmetric=0" in _native.describe_build(col)
+    col.b = col.a
+    col.symmetry = 2
+    assert _native.lib().kermac_b200_describe_variant(ctypes.byref(col), ctypes.create_string_buffer(64), 64) == -4
+    col.symmetry = 0
     col.inner_power = _native.POW_SQRT
     assert "variant=cpasync" in _native.describe_build(col) and "a_vec16=1" in _native.describe_build(col)
 

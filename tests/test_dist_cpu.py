@@ -68,6 +68,20 @@ def _worker(rank, world, port, n_total, results):
         yref = ko.kernel_matvec_ref(a, b, c, inner_operator="DIFF", inner_power="SQUARE", outer_power="SQRT",
                                     kernel_type="LAPLACE", bandwidth=8.0)[0].float()
         ok = ok and torch.equal(y, yref)
+
+        # gradient sharded over the rows of b and d: a (K, M), b (N, K), c (O, K), d (N, M)
+        ga = torch.rand(9, 33, generator=g)
+        gc = torch.randn(3, 9, generator=g)
+        gd = torch.randn(n_total, 33, generator=g)
+
+        def grad_compute(a_, b_, c_, d_, out):
+            out.copy_(ko.cdist_grad_ref(a_, b_, c_, d_, p=1.5)[0].float())
+
+        gref = ko.cdist_grad_ref(ga, b, gc, gd, p=1.5)[0].float()
+        gfull = kdist.cdist_grad_sharded(ga, b, gc, gd, p=1.5, compute=grad_compute)
+        gslab = kdist.cdist_grad_sharded(ga, b, gc, gd, p=1.5, compute=grad_compute, gather=False)
+        g0, g1 = kdist.shard_rows(n_total, rank, world, kdist.GRAD_ROW_ALIGN)
+        ok = ok and torch.equal(gfull, gref) and torch.equal(gslab, gref[:, g0:g1])
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()

@@ -52,6 +52,14 @@ def _worker(rank, world, port, results):
         y1 = kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=8.0,
                                   regularization=0.25, regularization_offset_x=300)[0]
         ok = ok and torch.equal(y, y1)
+        # gradient sharded over the rows of b and d
+        ga = torch.rand(96, 260, generator=g).cuda()
+        gc = torch.randn(4, 96, generator=g).cuda()
+        gd = torch.randn(1000, 260, generator=g).cuda()
+        for p in (1.0, 1.5):
+            full = kdist.cdist_grad_sharded(ga, b.contiguous(), gc, gd, p=p)
+            single = kermac.cdist_grad(ga, b.contiguous(), gc, gd, p=p)[0]
+            ok = ok and torch.equal(full, single)
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
