@@ -358,6 +358,13 @@ def main():
             t = max_over_ranks(timed_steps(compute_step(p), steps, 1, barrier)) / steps
             also[f"p={p:g}"] = {"ms_per_step": t, "value": ops_total / (t * 1e-3), "unit": "diff-ops/s",
                                 "note": "compute only (no gather)"}
+        if world == 1 and M == N:
+            # the same matrix on both sides: one triangle of tiles is computed and mirrored
+            def self_step():
+                kermac.cdist(a, a, out=slab.t(), p=args.p)
+            t = timed_steps(self_step, args.steps, 1, barrier) / args.steps
+            also[f"p={args.p:g} cdist(a, a)"] = {"ms_per_step": t, "value": ops_total / (t * 1e-3), "unit": "diff-ops/s",
+                                                 "note": "a and b the same matrix: symmetric build, 3*M*N*K still counted"}
         line["also"] = also
 
     if not args.no_e2e:
