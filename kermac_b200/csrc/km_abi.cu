@@ -66,6 +66,10 @@ const char* kermac_b200_last_error(void) { return km::g_last_error; }
 
 int kermac_b200_abi_version(void) { return KERMAC_B200_ABI_VERSION; }
 
-const char* kermac_b200_build_id(void) { return "kermac_b200 abi " "1" " sm_100a " __DATE__ " " __TIME__; }
+#define KM_STR2(x) #x
+#define KM_STR(x) KM_STR2(x)
+const char* kermac_b200_build_id(void) {
+    return "kermac_b200 abi " KM_STR(KERMAC_B200_ABI_VERSION) " sm_100a " __DATE__ " " __TIME__;
+}
 
 }  // extern "C"

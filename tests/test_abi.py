@@ -21,6 +21,7 @@ def test_library_loads_and_reports_abi_version():
     lib = _native.lib()
     assert lib.kermac_b200_abi_version() == _native.ABI_VERSION
     assert b"sm_100a" in lib.kermac_b200_build_id()
+    assert b"abi %d " % _native.ABI_VERSION in lib.kermac_b200_build_id()
 
 
 def test_every_declared_entry_point_is_exported():
