@@ -58,7 +58,9 @@ def check(res, prog=None):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    here = os.path.dirname(os.path.abspath(__file__))
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get(
+        "KERMAC_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(here)), "reference"))
     cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
     opts = [b"-std=c++17", b"-arch=sm_100", b"-default-device", b"-diag-suppress=64,1055",
             f"-I{ref}/include".encode(), f"-I{ref}/thirdparty/cutlass/include".encode(),
