@@ -26,6 +26,23 @@ def test_slab_sizes_cover_and_align():
         kdist.slab_sizes(10, 0)
 
 
+def test_sharded_helpers_without_a_process_group_run_the_whole_problem():
+    from oracle import kermac_oracle as ko
+    g = torch.Generator().manual_seed(5)
+    a, b, c, d = torch.rand(7, 20, generator=g), torch.randn(33, 7, generator=g), torch.randn(2, 7, generator=g), \
+        torch.randn(33, 20, generator=g)
+
+    def grad_compute(a_, b_, c_, d_, out):
+        out.copy_(ko.cdist_grad_ref(a_, b_, c_, d_, p=1.0)[0].float())
+
+    full = kdist.cdist_grad_sharded(a, b, c, d, p=1.0, compute=grad_compute)
+    assert torch.equal(full, ko.cdist_grad_ref(a, b, c, d, p=1.0)[0].float())
+    with pytest.raises(ValueError):
+        kdist.cdist_grad_sharded(a, b, c, d[:30], p=1.0, compute=grad_compute)
+    with pytest.raises(ValueError):
+        kdist.cdist_grad_sharded(a.unsqueeze(0), b, c, d, compute=grad_compute)
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
