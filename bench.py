@@ -1,21 +1,32 @@
-"""Benchmark of the cdist hot path on B200.
+"""Benchmark of the fused distance hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--p 1.0]
 
-One "step" is one full cdist over the headline workload: a[K=1024, M=30000], b[K=1024,
-N=30000], float32, entries N(0,1) from seed 1, out[N, M] (3.6 GB), epilogue on.  The
-default p is 1.0; p = 2.0 and p = 1.3 on the same inputs are measured too and reported
-under "also".  At N > 1 GPUs the output rows are sharded over ranks (fixed total work:
-strong scaling) and the step ends with an all-gather of the row slabs.
+One "step" of the headline is one full cdist over a[K=1024, M=30000], b[K=1024, N=30000],
+float32, entries N(0,1) from seed 1, out[N, M] (3.6 GB), epilogue on, default p = 1.0.  At
+N > 1 GPUs the output is sharded over ranks (fixed total work: strong scaling) and the step
+ends with the full result present on every rank.
 
 Prints ONE JSON line (rank 0):
-  value      difference-ops per second, 3*M*N*K per step, inputs resident on the device
-  e2e        same metric through kermac_b200.HostCdist: pinned host inputs copied in, result
-             copied out to pinned host memory, every step
-  roofline   the cdist kernel against the FP32 pipe peak measured on this device
+  value         difference-ops per second, 3*M*N*K per step, inputs resident on the device
+  e2e           same metric through kermac_b200.HostCdist: pinned host inputs copied in, result
+                copied out to pinned host memory, every step
+  roofline      the cdist kernel against the FP32 pipe peak measured on this device
   cpu_baseline  torch.cdist float32 on the host cores over a bounded row slab
-`--impl reference` times that CPU arm alone (the reference has no CPU implementation of
-its own; torch.cdist is what its tests and README compare against).
+  also          every other benchmark configuration, outside the headline's timed region, each
+                with ms_per_step, value and its own roofline:
+                  the same inputs at p = 2 and p = 1.3, cdist(a, a);
+                  the small 2048 x 2048 x 64 case (latency);
+                  the batched fractional-p case with and without the epilogue;
+                  cdist_grad at p = 1 and p = 1.5;
+                  kernel_matvec at M = N = 10^6, rows sharded over the ranks, all-gather included;
+                  ref_gpu: the reference's own CUDA kernels (compiled from its sources into
+                  baseline/_ref by baseline/build_ref_cubin.py) on the same inputs and GPU
+  verified      (N > 1) every rank compares sampled rows of every peer's part of the exchanged
+                results with its own single-GPU computation of those rows, and reports its
+                device error flag
+`--impl reference` times the CPU arm alone (the reference has no CPU implementation of its own;
+torch.cdist is what its tests and README compare against).
 """
 from __future__ import annotations
 
@@ -54,14 +65,19 @@ def parse_args():
     ap.add_argument("--m", type=int, default=M_DIM)
     ap.add_argument("--n", type=int, default=N_DIM)
     ap.add_argument("--k", type=int, default=K_DIM)
-    ap.add_argument("--no-also", action="store_true", help="skip the p=2 / p=1.3 side measurements")
+    ap.add_argument("--no-also", action="store_true", help="skip every side measurement")
+    ap.add_argument("--no-configs", action="store_true",
+                    help="keep the p=2 / p=1.3 side measurements but skip the other benchmark configurations")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-ref-gpu", action="store_true")
     ap.add_argument("--cpu-rows", type=int, default=512)
-    ap.add_argument("--workload", default="cdist", choices=["cdist", "cdist_batched", "grad", "matvec"],
-                    help="cdist is the headline workload; the others cover the remaining operators")
+    ap.add_argument("--workload", default="cdist",
+                    choices=["cdist", "cdist_small", "cdist_batched", "grad", "matvec"],
+                    help="cdist is the headline workload; the others run one of the remaining configurations alone")
     ap.add_argument("--mv-m", type=int, default=1_000_000, help="matvec: number of points a")
     ap.add_argument("--mv-n", type=int, default=1_000_000, help="matvec: number of points b")
+    ap.add_argument("--mv-steps", type=int, default=2, help="matvec: timed steps (one step is seconds at full size)")
     return ap.parse_args()
 
 
@@ -70,6 +86,17 @@ def make_inputs(m, n, k):
     a_store = torch.randn(k, m, generator=g, dtype=torch.float32)
     b_store = torch.randn(k, n, generator=g, dtype=torch.float32)
     return a_store, b_store
+
+
+def use_all_host_threads():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to every rank; the CPU arms are meant to
+    use the cores this process may run on, at every N."""
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    torch.set_num_threads(max(1, cores))
+    return torch.get_num_threads()
 
 
 class ClockSampler:
@@ -137,6 +164,7 @@ def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    threads = use_all_host_threads()
     from oracle import cpu_baseline
     a_store, b_store = make_inputs(args.m, args.n, args.k)
     rows = min(args.cpu_rows, args.n)
@@ -153,7 +181,7 @@ def reference_arm(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": config_dict(args, args.gpus),
-        "cpu_baseline": {"value": value, "unit": "diff-ops/s", "cores": torch.get_num_threads(),
+        "cpu_baseline": {"value": value, "unit": "diff-ops/s", "cores": threads,
                          "kind": "port", "sample": r["sample"]},
         "e2e": {"value": value, "unit": "diff-ops/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -182,8 +210,9 @@ def config_dict(args, world):
             else f"cdist fp32 a[K={args.k},M={args.m}] b[K={args.k},N={args.n}] N(0,1) seed 1",
             "p": args.p, "M": args.m, "N": args.n, "K": args.k,
             "sharding": "single GPU" if world == 1 else
-            f"output rows N in contiguous slabs over {world} ranks; the kernel writes its rows to the NVSwitch "
-            "multicast address of the result buffer (multimem.st), so every rank holds the full result when it ends",
+            f"the 128 x 128 output tiles in equal contiguous runs over {world} ranks; the kernel writes its tiles to "
+            "the NVSwitch multicast address of the result buffer (multimem.st), so every rank holds the full result "
+            "when it ends",
             "l2": "inputs (246 MB) and output (3.6 GB) exceed the 126 MB L2; no flush needed between steps",
             "vs_baseline_is": "value / the best kermac.cdist throughput the reference publishes for this size and p "
                               "(README table: %s ms on %s)" % PUBLISHED_MS.get(args.p, ("n/a", "n/a"))}
@@ -213,6 +242,37 @@ def emit(line):
 _REAL_STDOUT = os.dup(1)
 
 
+class Pipes:
+    """Arithmetic-pipe rates of this device at the clocks it runs at now (register-only kernels)."""
+
+    def __init__(self, native):
+        self.lane_packed = native.measure_pipe(1, 8192)[0]
+        self.lane_scalar = native.measure_pipe(0, 8192)[0]
+        self.mufu = native.measure_pipe(2, 2048)[0]
+        self.lane = max(self.lane_packed, self.lane_scalar)
+        self.loop_p2 = native.measure_pipe(4, 2048)[0]
+        self.loop_p1 = native.measure_pipe(5, 2048)[0]
+
+
+def cdist_roofline(p, ops, seconds, pipes):
+    """Roofline dict of one cdist launch that performed `ops` difference-ops in `seconds`."""
+    import bench_workloads
+    achieved = ops / seconds
+    if p in (1.0, 2.0):
+        loop = pipes.loop_p1 if p == 1.0 else pipes.loop_p2
+        return {
+            "bound": "fp32_simt", "achieved": achieved / 1e12, "peak": 2.0 * pipes.lane / 1e12,
+            "unit": "TFLOP/s (difference-ops)", "frac": achieved / (2.0 * pipes.lane),
+            "peak_source": "measured on this device by kermac_b200_measure_pipe (fma.rn.f32x2 chains), x2 flop per lane-op",
+            "frac_of_nominal_74.45": achieved / (148 * 128 * 2 * 1.965e9),
+            "fma_pipe_lane_utilisation": (2.0 / 3.0) * achieved / pipes.lane,
+            "inner_loop_ceiling_lane_ops": loop,
+            "frac_of_inner_loop_ceiling": (2.0 / 3.0) * achieved / loop,
+            "lane_ops_scalar": pipes.lane_scalar, "lane_ops_packed": pipes.lane_packed,
+        }
+    return bench_workloads.fractional_roofline(ops / 3.0, seconds, pipes)
+
+
 def main():
     args = parse_args()
     sys.stdout.flush()
@@ -235,6 +295,7 @@ def main():
     import kermac_b200 as kermac
     from kermac_b200 import _native, dist as kdist
     from kermac_b200.host import HostCdist
+    import bench_workloads
 
     def barrier():
         if world > 1:
@@ -247,21 +308,34 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    if args.workload != "cdist":
-        import bench_workloads
+    def all_ranks_ok(flag: bool) -> bool:
+        if world == 1:
+            return bool(flag)
+        t = torch.tensor([1 if flag else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
 
-        class Ctx:
-            pass
-        ctx = Ctx()
-        ctx.rank, ctx.world, ctx.barrier, ctx.max_over_ranks = rank, world, barrier, max_over_ranks
-        ctx.clocks = lambda: ClockSampler(local_rank)
-        line = getattr(bench_workloads, args.workload)(args, ctx)
+    class Ctx:
+        pass
+    ctx = Ctx()
+    ctx.rank, ctx.world, ctx.barrier, ctx.max_over_ranks, ctx.device = rank, world, barrier, max_over_ranks, device
+    ctx.clocks = lambda: ClockSampler(local_rank)
+    ctx.all_ranks_ok = all_ranks_ok
+    ctx.pipes = None
+
+    def finish(line):
+        # a bounded wait that ran out on ANY rank leaves stale rows behind: every rank reads its own flag
+        clean = all_ranks_ok(_native.device_error_flag() == 0)
         if rank == 0:
-            assert _native.device_error_flag() == 0, "a bounded wait inside a kernel ran out"
+            assert clean, "a bounded wait inside a kernel ran out on some rank"
             emit(line)
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
+
+    if args.workload != "cdist":
+        line = getattr(bench_workloads, args.workload)(args, ctx)
+        finish(line)
         return
 
     M, N, K = args.m, args.n, args.k
@@ -271,7 +345,7 @@ def main():
     launches = {"n": 0}
     if world == 1:
         start, stop = 0, N
-        my_rows = N
+        share = 1.0
         slab = torch.empty((N, M), dtype=torch.float32, device=device)
 
         def compute_step(p):
@@ -282,11 +356,11 @@ def main():
 
         job_step = compute_step
     else:
-        # contiguous row slab per rank, computed in a few launches; finished rows are pushed to
-        # the peers by copy engines over NVLink while the next launch computes
+        # one launch per rank over its run of output tiles; the kernel's stores go to the multicast
+        # address of the symmetric result buffer, so the exchange happens while it computes
         cyc = kdist.OverlappedCdist(M, N, device, chunks=int(os.environ.get("KM_DIST_CHUNKS", "8")),
                                     transport=os.environ.get("KM_DIST_TRANSPORT", "auto"))
-        my_rows = cyc.rows
+        share = cyc.work_share()
         start, stop = kdist.shard_rows(N, rank, world, kdist.ROW_ALIGN)
         slab = None
 
@@ -297,7 +371,6 @@ def main():
             return lambda: cyc.run(a, b, p=p, gather=True)
 
     ops_total = 3.0 * M * N * K
-    results = {}
     with ClockSampler(local_rank) as clocks:
         launches["n"] = 0
         if world > 1:
@@ -309,9 +382,10 @@ def main():
     value = ops_total / (ms_per_step * 1e-3)
     clock_info = clocks.summary()
 
-    # kernel-only time (no gather) on this rank's slab, for the roofline
+    # kernel-only time (no exchange) on this rank's share, for the roofline
     k_ms = max_over_ranks(timed_steps(compute_step(args.p), args.steps, 1, barrier)) / args.steps
-    slab_ops = 3.0 * M * my_rows * K
+    share = max_over_ranks(share)          # the slowest rank is the one with the largest share
+    share_ops = ops_total * share
 
     line = {
         "metric": metric_name(args.p), "value": value, "unit": "diff-ops/s", "n_gpus": world,
@@ -319,45 +393,30 @@ def main():
         "scaling": "strong", "vs_baseline": vs_published(args, world, value), "dtype": "f32", "data": "synthetic",
         "config": config_dict(args, world), "clocks": clock_info, "gpu_launches": timed_launches,
         "compute_only": {"ms_per_step": k_ms, "value": ops_total / (k_ms * 1e-3),
-                         "note": "cdist kernel on this rank's row slab, max over ranks, no gather"},
+                         "note": "cdist kernel on this rank's share of the output, max over ranks, no exchange"},
     }
+    if world > 1:
+        line["config"]["transport"] = cyc.transport
+        line["config"]["partition"] = cyc.partition
 
-    if rank == 0:
-        # FP32 pipe peak of this device at the clocks it runs at now (register-only FMA chains)
-        lane_ops_packed, _ = _native.measure_pipe(1, 8192)
-        lane_ops_scalar, _ = _native.measure_pipe(0, 8192)
-        mufu_ops, _ = _native.measure_pipe(2, 2048)
-        lane_peak = max(lane_ops_packed, lane_ops_scalar)
-        fp32_peak_flops = 2.0 * lane_peak
-        # what the inner loop's instruction mix sustains with operands already in shared memory
-        ceiling_lane_ops, _ = _native.measure_pipe(5 if args.p == 1.0 else 4, 2048)
-        achieved = slab_ops / (k_ms * 1e-3)
-        nominal = 148 * 128 * 2 * 1.965e9
-        line["roofline"] = {
-            "bound": "fp32_simt" if args.p in (1.0, 2.0) else "mufu",
-            "achieved": achieved / 1e12, "peak": fp32_peak_flops / 1e12, "unit": "TFLOP/s (difference-ops)",
-            "frac": achieved / fp32_peak_flops,
-            "peak_source": "measured on this device by kermac_b200_measure_pipe (fma.rn.f32x2 chains), x2 flop per lane-op",
-            "frac_of_nominal_74.45": achieved / nominal,
-            "fma_pipe_lane_utilisation": (2.0 / 3.0) * achieved / lane_peak,
-            "inner_loop_ceiling_lane_ops": ceiling_lane_ops,
-            "frac_of_inner_loop_ceiling": (2.0 / 3.0) * achieved / ceiling_lane_ops,
-            "mufu_peak_ops": mufu_ops, "mufu_utilisation": (2.0 / 3.0) * achieved / mufu_ops,
-            "lane_ops_scalar": lane_ops_scalar, "lane_ops_packed": lane_ops_packed,
-            "traffic": TRAFFIC_BYTES_PER_LAUNCH if (M, N, K) == (M_DIM, N_DIM, K_DIM) and world == 1 else None,
-            "traffic_note": TRAFFIC_NOTE,
-            "hbm_gbs_algorithmic": 4.0 * (M * my_rows + K * (M + my_rows)) / (k_ms * 1e-3) / 1e9,
-        }
+    pipes = Pipes(_native)
+    ctx.pipes = pipes
+    roof = cdist_roofline(args.p, share_ops, k_ms * 1e-3, pipes)
+    roof["traffic"] = TRAFFIC_BYTES_PER_LAUNCH if (M, N, K) == (M_DIM, N_DIM, K_DIM) and world == 1 else None
+    roof["traffic_note"] = TRAFFIC_NOTE
+    roof["hbm_gbs_algorithmic"] = 4.0 * (M * N * share + K * (M + N * share)) / (k_ms * 1e-3) / 1e9
+    line["roofline"] = roof
 
+    also = {}
     if not args.no_also:
-        also = {}
         for p in (2.0, 1.3):
             if p == args.p:
                 continue
             steps = args.steps if p == 2.0 else max(2, args.steps // 3)
             t = max_over_ranks(timed_steps(compute_step(p), steps, 1, barrier)) / steps
             also[f"p={p:g}"] = {"ms_per_step": t, "value": ops_total / (t * 1e-3), "unit": "diff-ops/s",
-                                "note": "compute only (no gather)"}
+                                "note": "compute only (no exchange)",
+                                "roofline": cdist_roofline(p, share_ops, t * 1e-3, pipes)}
         if world == 1 and M == N:
             # the same matrix on both sides: one triangle of tiles is computed and mirrored
             def self_step():
@@ -365,7 +424,11 @@ def main():
             t = timed_steps(self_step, args.steps, 1, barrier) / args.steps
             also[f"p={args.p:g} cdist(a, a)"] = {"ms_per_step": t, "value": ops_total / (t * 1e-3), "unit": "diff-ops/s",
                                                  "note": "a and b the same matrix: symmetric build, 3*M*N*K still counted"}
-        line["also"] = also
+        if world == 1 and not args.no_ref_gpu:
+            also["ref_gpu"] = bench_workloads.ref_gpu_cdist(a, b, slab, also, args.p, ms_per_step, ops_total)
+
+    if world > 1:
+        line["verified"] = bench_workloads.verify_sharded(ctx, cyc, a, b)
 
     if not args.no_e2e:
         pipe = HostCdist(M, stop - start, K, device=device, slabs=16)
@@ -374,7 +437,7 @@ def main():
         out_pin = torch.empty((stop - start, M), dtype=torch.float32).pin_memory()
         slab = None
         if world > 1:
-            cyc.full = None
+            cyc.release()
         torch.cuda.empty_cache()
 
         def e2e_step():
@@ -394,19 +457,32 @@ def main():
         line["e2e"] = {"value": ops_total / (e_ms * 1e-3), "unit": "diff-ops/s", "ms_per_step": e_ms,
                        "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes,
                        "steps": e_steps,
-                       "note": "kermac_b200.host.HostCdist: pinned host a, b in; out[N,M] slab back to pinned host; "
-                               "bytes are per rank"}
+                       "note": "kermac_b200.host.HostCdist: pinned host a, b in; this rank's rows of out[N,M] back to "
+                               "pinned host; bytes are per rank"}
+        del pipe, a_pin, b_pin, out_pin
+
+    # the remaining benchmark configurations, each outside the headline's timed region
+    slab = None
+    if world > 1:
+        cyc.release()
+    del a, b, a_dev, b_dev
+    torch.cuda.empty_cache()
+    if not args.no_also and not args.no_configs:
+        args.no_e2e_side = True
+        if world == 1:
+            also["cfg1 cdist 2048x2048x64 p=2"] = bench_workloads.brief(bench_workloads.cdist_small(args, ctx))
+            also["cfg3 cdist batched p=1.3"] = bench_workloads.brief(bench_workloads.cdist_batched(args, ctx))
+            also["cfg4 cdist_grad"] = bench_workloads.brief(bench_workloads.grad(args, ctx))
+        also["cfg5 kernel_matvec"] = bench_workloads.brief(bench_workloads.matvec(args, ctx))
+    if also:
+        line["also"] = also
 
     if rank == 0 and not args.no_cpu:
         from oracle import cpu_baseline
+        use_all_host_threads()
         line["cpu_baseline"] = cpu_baseline.time_cdist_slab(a_store, b_store, args.p, rows=args.cpu_rows, repeats=3,
                                                             budget_s=20.0)
-    if rank == 0:
-        assert _native.device_error_flag() == 0, "a bounded wait inside a kernel ran out"
-        emit(line)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    finish(line)
 
 
 if __name__ == "__main__":

@@ -42,7 +42,7 @@
 extern "C" {
 #endif
 
-#define KERMAC_B200_ABI_VERSION 4
+#define KERMAC_B200_ABI_VERSION 5
 
 /* Rejected preconditions (negative return codes). */
 #define KM_ERR_NULL_POINTER   (-1)
@@ -113,6 +113,14 @@ typedef struct KmBuildArgs {
                                  computed and each is also written transposed: half the arithmetic, bit-identical
                                  results (equal to rounding for |.|^p, whose exp2 takes one of two routes).  KM_SYMMETRY_OFF computes every tile.  The reference declares a Symmetry
                                  enum (src/kermac/build_a_kernel.py:35-37) that nothing uses. */
+    int32_t tile_first;       /* This call computes only the output tiles [tile_first, tile_first + tile_count) of */
+    int32_t tile_count;       /* the launcher's linear order of 128 x 128 tiles (kermac_b200_build_tile_count gives
+                                 the total); tile_count 0 = every tile from tile_first on.  Calls whose ranges
+                                 partition [0, total) together write every element of `out` exactly once, which
+                                 is how several GPUs share one problem in equal parts whatever its shape (with
+                                 out_multicast each GPU's tiles land in every GPU's buffer).  A partial range
+                                 switches the symmetric plan off.  The reference always launches the full grid
+                                 (src/kermac/build_a_kernel.py:348-353). */
 } KmBuildArgs;
 
 #define KM_SYMMETRY_AUTO 0
@@ -124,6 +132,12 @@ typedef struct KmBuildArgs {
 #define KM_VARIANT_TMA      2   /* TMA + mbarrier, needs m-contiguous 16-byte aligned a and b */
 
 int kermac_b200_build_kernel(const KmBuildArgs* args, void* stream);
+
+/* Number of 128 x 128 output tiles of one batch entry of this problem: the extent of the
+ * linear tile order that tile_first / tile_count index.  Negative KM_ERR_* code when the
+ * arguments are rejected.  Counterpart of the grid computation at
+ * src/kermac/build_a_kernel.py:348-353. */
+int64_t kermac_b200_build_tile_count(const KmBuildArgs* args);
 
 /*
  * out[l, o, n, m] = sum_k c[l, o, k] * a[l, k, m] * g(d[l, n, m] - b[l, n, k])
@@ -162,15 +176,22 @@ int64_t kermac_b200_cdist_grad_scratch_bytes(const KmGradArgs* args);
  * layer that can only forward the pointers it was given).  The partial sums of the k
  * split go to an array that is part of the library image, KM_GRAD_STATIC_SCRATCH_BYTES
  * large, which every GPU that loads the library holds until the process exits.
- * args->scratch and args->scratch_bytes are ignored.  The call never allocates.
- *   - A problem whose k split (args->split_k, or the automatic choice when 0) needs more
- *     than KM_GRAD_STATIC_SCRATCH_BYTES is rejected with KM_ERR_TOO_LARGE; split_k = 1
+ * args->scratch and args->scratch_bytes are ignored.  The library makes no allocator call;
+ * the array itself is placed by the CUDA runtime when it loads the module on a device, which
+ * happens at the latest during the first call there, so make one warm-up call per device
+ * outside any region that must not reserve device memory.
+ *   - An explicit args->split_k > 1 whose partial sums need more than
+ *     KM_GRAD_STATIC_SCRATCH_BYTES is rejected with KM_ERR_TOO_LARGE.  With split_k = 0 the
+ *     automatic split is reduced to the largest one that fits, down to a single pass (the same
+ *     thing kermac_b200_cdist_grad does when the caller's scratch is too small); split_k = 1
  *     always fits (single pass, no scratch).
  *   - All calls share the one array and it keeps the previous call's contents.  Nothing
  *     in it needs clearing (each call writes every partial it later reads), but calls that
  *     overlap on the GPU race on it: order them on one stream or with events.
  *   - The first call on each device looks up the array's device address with the CUDA
- *     runtime; make that first call outside any stream capture.
+ *     runtime; make that first call outside any stream capture.  The address is kept for the
+ *     life of the process and does not survive cudaDeviceReset() or a teardown of the
+ *     device's primary context.
  * It has no counterpart in the reference.
  */
 #define KM_GRAD_STATIC_SCRATCH_BYTES (64LL << 20)
@@ -237,6 +258,13 @@ int kermac_b200_measure_pipe(int32_t kind, int32_t iterations, double* ops_per_s
  * Synchronises the current device.  Returns 0 (clear), 1 (a wait ran out) or a
  * negative code if the device could not be queried.  No reference counterpart. */
 int kermac_b200_device_error_flag(void);
+
+/* Test hook for the report path above: launches one block that waits `tries` (1 .. 2^20)
+ * attempts on an mbarrier nothing ever arrives at, gives up, raises the device error flag
+ * and ends.  The wait is bounded by construction; nothing faults or hangs.  After it,
+ * kermac_b200_device_error_flag() returns 1 once and then 0.  No reference counterpart
+ * (the reference's kernels have no waits on asynchronous units). */
+int kermac_b200_selftest_wait_expiry(int32_t tries, void* stream);
 
 const char* kermac_b200_last_error(void);
 int kermac_b200_abi_version(void);

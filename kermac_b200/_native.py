@@ -11,7 +11,7 @@ import os
 import threading
 from typing import Optional
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 # enum values of include/kermac_b200.h
 INNER_DIFF, INNER_DOT = 0, 1
@@ -22,6 +22,7 @@ VARIANT_AUTO, VARIANT_CPASYNC, VARIANT_TMA = 0, 1, 2
 
 EXPORTED_SYMBOLS = (
     "kermac_b200_build_kernel",
+    "kermac_b200_build_tile_count",
     "kermac_b200_cdist_grad",
     "kermac_b200_cdist_grad_scratch_bytes",
     "kermac_b200_cdist_grad_static",
@@ -30,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "kermac_b200_describe_variant",
     "kermac_b200_measure_pipe",
     "kermac_b200_device_error_flag",
+    "kermac_b200_selftest_wait_expiry",
     "kermac_b200_last_error",
     "kermac_b200_abi_version",
     "kermac_b200_build_id",
@@ -54,6 +56,8 @@ class KmBuildArgs(C.Structure):
         ("variant", C.c_int32),
         ("out_multicast", C.c_int32),
         ("symmetry", C.c_int32),
+        ("tile_first", C.c_int32),
+        ("tile_count", C.c_int32),
     ]
 
 
@@ -109,6 +113,10 @@ def library_path() -> str:
 def _declare(lib: C.CDLL) -> None:
     lib.kermac_b200_build_kernel.argtypes = [C.POINTER(KmBuildArgs), C.c_void_p]
     lib.kermac_b200_build_kernel.restype = C.c_int
+    lib.kermac_b200_build_tile_count.argtypes = [C.POINTER(KmBuildArgs)]
+    lib.kermac_b200_build_tile_count.restype = C.c_int64
+    lib.kermac_b200_selftest_wait_expiry.argtypes = [C.c_int32, C.c_void_p]
+    lib.kermac_b200_selftest_wait_expiry.restype = C.c_int
     lib.kermac_b200_cdist_grad.argtypes = [C.POINTER(KmGradArgs), C.c_void_p]
     lib.kermac_b200_cdist_grad.restype = C.c_int
     lib.kermac_b200_cdist_grad_scratch_bytes.argtypes = [C.POINTER(KmGradArgs)]
@@ -194,6 +202,19 @@ def hyper(value) -> KmHyper:
 
 def launch_build(args: KmBuildArgs, stream_ptr: int) -> None:
     check(lib().kermac_b200_build_kernel(C.byref(args), C.c_void_p(stream_ptr)), "kermac_b200_build_kernel")
+
+
+def build_tile_count(args: KmBuildArgs) -> int:
+    """Number of 128 x 128 output tiles of one batch entry: the range tile_first / tile_count index."""
+    n = int(lib().kermac_b200_build_tile_count(C.byref(args)))
+    if n < 0:
+        check(n, "kermac_b200_build_tile_count")
+    return n
+
+
+def selftest_wait_expiry(tries: int = 1024, stream_ptr: int = 0) -> None:
+    """Launches the one-block kernel whose bounded wait runs out on purpose (see the header)."""
+    check(lib().kermac_b200_selftest_wait_expiry(int(tries), C.c_void_p(stream_ptr)), "kermac_b200_selftest_wait_expiry")
 
 
 def launch_grad(args: KmGradArgs, stream_ptr: int) -> None:

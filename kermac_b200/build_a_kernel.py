@@ -304,6 +304,10 @@ def run_kernel(
     tensor hyper-parameters must be 1 or agree; extent-1 operands broadcast.  When `out`
     is None a (L, M, N) tensor is allocated.  Launches on torch's current stream and
     returns without synchronising.
+
+    The TMA-staged kernels wait on their copies with a bound; if such a wait ever runs out the
+    affected tiles are not written and a device flag is raised.  Nothing here reads it: poll
+    `kermac_b200._native.device_error_flag()` at your own synchronisation points (0 = clean).
     """
     args, out, keep_alive = _marshal_build(
         kernel_descriptor, a, b, out, p, inner_p, outer_p, bandwidth, epsilon, regularization,

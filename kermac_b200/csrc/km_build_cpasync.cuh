@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(CPA_THREADS, 2) build_cpasync_kernel(const __g
     const int l    = blockIdx.y;
 
     int tm, tn;
-    tile_coords(blockIdx.x, p.tiles_m, p.tiles_n, p.panel, tm, tn);
+    tile_coords(p.tile_first + blockIdx.x, p.tiles_m, p.tiles_n, p.panel, tm, tn);
     if (SYM && tn < tm) return;   // the tile's mirror image (tn, tm) writes this part of C
     const int m0 = tm * CPA_TILE;
     const int n0 = tn * CPA_TILE;

@@ -107,6 +107,14 @@ int make_plan(const KmBuildArgs* a, BuildPlan* plan) {
     if (a->out_multicast != 0 && a->out_multicast != 1)
         return fail(KM_ERR_BAD_ENUM, "out_multicast must be 0 or 1");
     p.c_multicast = a->out_multicast;
+    const int total_tiles = p.tiles_m * p.tiles_n;
+    if (a->tile_first < 0 || a->tile_count < 0 || a->tile_first > total_tiles ||
+        (long long)a->tile_first + a->tile_count > total_tiles)
+        return fail(KM_ERR_BAD_SHAPE, "tile range [%d, %d + %d) is outside the %d tiles of this problem", a->tile_first,
+                    a->tile_first, a->tile_count, total_tiles);
+    p.tile_first = a->tile_first;
+    p.tile_count = a->tile_count > 0 ? a->tile_count : total_tiles - a->tile_first;
+    const bool all_tiles = (p.tile_first == 0 && p.tile_count == total_tiles);
 
     // a and b the same matrix, a chain that does not change when m and n trade places (the
     // diagonal rule included): compute the tiles on and above the diagonal and mirror them.
@@ -118,7 +126,7 @@ int make_plan(const KmBuildArgs* a, BuildPlan* plan) {
                              p.inner_id >= IN_DOT_NOOP);
     p.symmetric = (a->symmetry == KM_SYMMETRY_AUTO) && even_chain && p.M == p.N && p.tiles_m > 1 && p.A == p.B &&
                   p.a_sm == p.b_sn && p.a_sk == p.b_sk && p.a_sl == p.b_sl && p.reg_off_m == p.reg_off_n &&
-                  !p.c_multicast;
+                  !p.c_multicast && all_tiles;
 
     plan->avec = (p.a_sm == 1) && aligned16(p.A) && (p.a_sk % 4 == 0 || p.K <= 1) && (p.a_sl % 4 == 0);
     plan->bvec = (p.b_sn == 1) && aligned16(p.B) && (p.b_sk % 4 == 0 || p.K <= 1) && (p.b_sl % 4 == 0);
@@ -143,7 +151,7 @@ extern "C" int kermac_b200_build_kernel(const KmBuildArgs* args, void* stream) {
     BuildPlan plan;
     if (int rc = make_plan(args, &plan)) return rc;
     BuildParams& p = plan.p;
-    if (p.M == 0 || p.N == 0) return 0;
+    if (p.M == 0 || p.N == 0 || p.tile_count == 0) return 0;
     if (int rc = require_sm100()) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
@@ -165,11 +173,21 @@ extern "C" int kermac_b200_build_kernel(const KmBuildArgs* args, void* stream) {
         if (q.p_outer.ptr) q.p_outer.ptr += (long long)l0 * q.p_outer.batch_stride;
         if (q.bandwidth.ptr) q.bandwidth.ptr += (long long)l0 * q.bandwidth.batch_stride;
         if (q.regularization.ptr) q.regularization.ptr += (long long)l0 * q.regularization.batch_stride;
-        dim3 grid((unsigned)(q.tiles_m * q.tiles_n), (unsigned)q.L, 1);
+        dim3 grid((unsigned)q.tile_count, (unsigned)q.L, 1);
         fn<<<grid, BUILD_CPA_THREADS, BUILD_CPA_SMEM_BYTES, st>>>(q);
         if (int rc = cuda_status(cudaGetLastError(), "launch of build_cpasync_kernel")) return rc;
     }
     return 0;
+}
+
+extern "C" int64_t kermac_b200_build_tile_count(const KmBuildArgs* args) {
+    using namespace km;
+    if (!args) return fail(KM_ERR_NULL_POINTER, "args is NULL");
+    KmBuildArgs whole = *args;
+    whole.tile_first = whole.tile_count = 0;
+    BuildPlan plan;
+    if (int rc = make_plan(&whole, &plan)) return rc;
+    return (int64_t)plan.p.tiles_m * plan.p.tiles_n;
 }
 
 extern "C" int kermac_b200_describe_variant(const KmBuildArgs* args, char* buf, int32_t buf_len) {
@@ -180,8 +198,9 @@ extern "C" int kermac_b200_describe_variant(const KmBuildArgs* args, char* buf, 
     const BuildParams& p = plan.p;
     snprintf(buf, (size_t)buf_len,
              "build_kernel variant=%s inner=%s outer_power=%d kernel_type=%d exchanged=%d a_vec16=%d b_vec16=%d "
-             "out_vec16=%d tiles=%dx%d batches=%d symmetric=%d",
+             "out_vec16=%d tiles=%dx%d batches=%d symmetric=%d tile_range=%d+%d",
              plan.variant == KM_VARIANT_TMA ? "tma" : "cpasync", kInnerNames[p.inner_id], p.outer_power, p.kernel_type,
-             plan.swapped ? 1 : 0, plan.avec ? 1 : 0, plan.bvec ? 1 : 0, p.c_vec4, p.tiles_m, p.tiles_n, p.L, p.symmetric);
+             plan.swapped ? 1 : 0, plan.avec ? 1 : 0, plan.bvec ? 1 : 0, p.c_vec4, p.tiles_m, p.tiles_n, p.L, p.symmetric,
+             p.tile_first, p.tile_count);
     return 0;
 }

@@ -31,6 +31,8 @@ struct BuildParams {
     float sgn;                      // -1 when A and B were exchanged, else +1
     int   tiles_m, tiles_n;         // 128 x 128 output tiles
     int   panel;                    // rasterisation: n-tiles per panel
+    int   tile_count;               // thread blocks (tiles) of this launch per batch entry
+    int   tile_first;               // linear index of the tile that block 0 computes (a launch may cover a sub-range)
     int   c_vec4;                   // C rows may be written with 16-byte stores
     int   c_multicast;              // C is an NVSwitch multicast address: write with multimem.st
     int   symmetric;                // A and B are the same matrix and the chain is symmetric in (m, n):

@@ -58,7 +58,7 @@ build_tma_kernel(const __grid_constant__ BuildParams p, const __grid_constant__ 
     const int l    = blockIdx.y;
 
     int tm, tn;
-    tile_coords(blockIdx.x, p.tiles_m, p.tiles_n, p.panel, tm, tn);
+    tile_coords(p.tile_first + blockIdx.x, p.tiles_m, p.tiles_n, p.panel, tm, tn);
     if (SYM && tn < tm) return;   // the tile's mirror image (tn, tm) writes this part of C
     const int m0 = tm * TMA_TILE;
     const int n0 = tn * TMA_TILE;
@@ -271,7 +271,7 @@ int launch_build_tma(const BuildParams& p, cudaStream_t stream) {
         CUtensorMap map_a, map_b;
         if (int rc = encode_operand(&map_a, q.A, q.M, q.K, q.L, q.a_sk, q.a_sl, kBK)) return rc;
         if (int rc = encode_operand(&map_b, q.B, q.N, q.K, q.L, q.b_sk, q.b_sl, kBK)) return rc;
-        dim3 grid((unsigned)(q.tiles_m * q.tiles_n), (unsigned)q.L, 1);
+        dim3 grid((unsigned)q.tile_count, (unsigned)q.L, 1);
         fn<<<grid, TMA_THREADS, kSmemBytes, stream>>>(q, map_a, map_b);
         if (int rc = cuda_status(cudaGetLastError(), "launch of build_tma_kernel")) return rc;
     }
@@ -279,6 +279,37 @@ int launch_build_tma(const BuildParams& p, cudaStream_t stream) {
 }
 
 }  // namespace km
+
+// The path a kernel takes when one of its bounded waits runs out, exercised on purpose and
+// safely: one block initialises an mbarrier that expects one arrival, nobody ever arrives,
+// thread 0 waits for `tries` attempts, gives up, records the fact in the same device flag the
+// build kernels use and the block ends.  Nothing faults or hangs: the loop is bounded by
+// construction and the barrier lives in the block's own shared memory.
+namespace km {
+namespace {
+__global__ void wait_expiry_selftest_kernel(int tries, int* gave_up) {
+    __shared__ __align__(8) unsigned long long bar;
+    const uint32_t bar_addr = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(bar_addr, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !mbar_wait_bounded(bar_addr, 0, tries)) {
+        atomicExch(&g_tma_wait_expired, 1);
+        if (gave_up) *gave_up = 1;
+    }
+}
+}  // namespace
+}  // namespace km
+
+extern "C" int kermac_b200_selftest_wait_expiry(int32_t tries, void* stream) {
+    using namespace km;
+    if (tries < 1 || tries > (1 << 20)) return fail(KM_ERR_BAD_SHAPE, "tries must be in [1, 2^20]");
+    if (int rc = require_sm100()) return rc;
+    wait_expiry_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(tries, nullptr);
+    return cuda_status(cudaGetLastError(), "launch of wait_expiry_selftest_kernel");
+}
 
 // Reads back (and clears) the flag that a bounded mbarrier wait sets when it runs
 // out.  Synchronises the device.  Returns 0 / 1, or a negative / CUDA error code.

@@ -423,7 +423,12 @@ extern "C" int kermac_b200_cdist_grad(const KmGradArgs* args, void* stream) {
 //     order them;
 //   * the first call on each device looks up the array's device address.  That lookup
 //     is a runtime API call, so make the first call per device outside any stream
-//     capture.
+//     capture.  The library calls no allocator, but the CUDA runtime places the array
+//     when it loads this module on a device (at the latest during that first call), so
+//     that warm-up call also belongs outside any region that must not see device memory
+//     being reserved;
+//   * the looked-up address is kept per device ordinal for the life of the process: it
+//     does not survive cudaDeviceReset() or the teardown of the device's primary context.
 namespace km {
 namespace {
 
@@ -462,15 +467,27 @@ extern "C" int kermac_b200_cdist_grad_static(const KmGradArgs* args, void* strea
     KmGradArgs local   = *args;
     local.scratch      = nullptr;
     local.scratch_bytes = 0;
-    // How much scratch the requested (or automatic) k split needs; 0 means a single pass.
-    const int64_t need = kermac_b200_cdist_grad_scratch_bytes(&local);
-    const int64_t cap  = KM_GRAD_STATIC_FLOATS * 4;
-    if (need > cap)
-        return fail(KM_ERR_TOO_LARGE,
-                    "this problem's k split needs %lld bytes of scratch but the built-in array holds %lld; "
-                    "pass split_k = 1, or call kermac_b200_cdist_grad with your own scratch",
-                    (long long)need, (long long)cap);
-    if (need > 0) {
+    GradPlan plan;
+    if (int rc = make_grad_plan(&local, &plan)) return rc;
+    const int64_t cap      = KM_GRAD_STATIC_FLOATS * 4;
+    const int64_t per_split = plan.partial_elems * 4;
+    if (local.split_k > 1) {
+        // an explicit split either fits the built-in array or is refused
+        const int64_t need = (int64_t)local.split_k * per_split;
+        if (need > cap)
+            return fail(KM_ERR_TOO_LARGE,
+                        "split_k = %d needs %lld bytes of scratch but the built-in array holds %lld; pass a smaller "
+                        "split_k (1 always fits), or call kermac_b200_cdist_grad with your own scratch",
+                        local.split_k, (long long)need, (long long)cap);
+    } else if (local.split_k == 0) {
+        // automatic: the preferred split, reduced to the largest one whose partial sums fit (down to a
+        // single pass), as kermac_b200_cdist_grad does when the caller's scratch is too small
+        long long fit = per_split > 0 ? cap / per_split : plan.splits_wanted;
+        int splits    = plan.splits_wanted;
+        if (splits > fit) splits = (int)fit;
+        local.split_k = splits > 1 ? splits : 1;
+    }
+    if (local.split_k > 1) {
         float* ptr = nullptr;
         if (int rc = grad_static_scratch(&ptr)) return rc;
         local.scratch       = ptr;

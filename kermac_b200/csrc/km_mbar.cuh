@@ -28,10 +28,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, int parity) {
         : "memory");
     return done != 0;
 }
-// Waits for the phase of `bar` with the given parity; gives up after a bounded
-// number of attempts (seconds at most) and returns false.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, int parity) {
-    for (int i = 0; i < (1 << 22); ++i)
+// Waits for the phase of `bar` with the given parity; gives up after `tries` attempts
+// (the default amounts to seconds at most) and returns false.
+constexpr int MBAR_WAIT_TRIES = 1 << 22;
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, int parity, int tries = MBAR_WAIT_TRIES) {
+    for (int i = 0; i < tries; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }

@@ -16,7 +16,7 @@ from typing import Callable, Optional, Tuple
 import torch
 import torch.distributed as dist_
 
-__all__ = ["shard_rows", "slab_sizes", "gather_buffer", "gather_rows_inplace", "gather_rows", "cdist_sharded",
+__all__ = ["shard_rows", "slab_sizes", "tile_ranges", "tile_coords", "gather_buffer", "gather_rows_inplace", "gather_rows", "cdist_sharded",
            "OverlappedCdist", "kernel_matvec_sharded", "cdist_grad_sharded"]
 
 
@@ -92,7 +92,8 @@ def gather_rows(local: torch.Tensor, n_total: int, group=None, align: int = 1) -
 
 def cdist_sharded(a: torch.Tensor, b: torch.Tensor, p: float = 2.0, skip_epilogue: bool = False,
                   group=None, gather: bool = True, compute: Optional[Callable] = None) -> torch.Tensor:
-    """Row-sharded `cdist` for 2-D operands.
+    """Row-sharded `cdist` for 2-D operands (bit-identical to the single-GPU result for p = 1 and
+    p = 2; to rounding for fractional p when a row lands at another position of its tile).
 
     Every rank passes the same `a` (M, K) and `b` (N, K).  Returns distances in storage
     order [n][m]: the full (N, M) tensor when `gather`, else this rank's (rows_r, M) slab.
@@ -121,26 +122,70 @@ def cdist_sharded(a: torch.Tensor, b: torch.Tensor, p: float = 2.0, skip_epilogu
     return gather_rows_inplace(buf, n_total, group)
 
 
+def tile_ranges(total: int, world: int) -> list:
+    """[(first, count)] per rank: `total` work units in contiguous runs that differ by at most one."""
+    if world < 1:
+        raise ValueError("world must be >= 1")
+    if total < 0:
+        raise ValueError("total must be >= 0")
+    base, extra = divmod(total, world)
+    out, first = [], 0
+    for r in range(world):
+        count = base + (1 if r < extra else 0)
+        out.append((first, count))
+        first += count
+    return out
+
+
+TILE = 128          # edge of an output tile of the build kernels
+TILE_PANEL = 16     # tile columns (n) per raster panel of the launcher's tile order
+
+
+def tile_coords(t: int, tiles_m: int, tiles_n: int, panel: int = TILE_PANEL) -> Tuple[int, int]:
+    """(tile_m, tile_n) of position t in the build launcher's linear tile order: panels of `panel`
+    tile columns, each walked row by row.  Host mirror of the device function of the same name
+    (kermac_b200/csrc/km_build_params.cuh), for callers that want to know which part of the output
+    a tile range covers."""
+    per_panel = panel * tiles_m
+    pidx, r = divmod(t, per_panel)
+    n0 = pidx * panel
+    width = min(panel, tiles_n - n0)
+    tm, rest = divmod(r, width)
+    return tm, n0 + rest
+
+
 class OverlappedCdist:
-    """Row-sharded `cdist` that moves the result to the other ranks while it is computed.
+    """Sharded `cdist` that moves the result to the other ranks while it is computed.
 
-    Rank r owns the contiguous slab of rows `shard_rows(N, r, world, 128)` of the result
-    [n][m].  The slab is computed in `chunks` launches; as soon as a launch is done, its
-    rows are pushed into the same rows of every peer's result buffer by peer-to-peer
-    copies, which the copy engines carry over NVLink without occupying an SM, while the
-    next launch computes.  Only the last chunk's push and one cross-rank barrier are not
-    hidden.  (A collective on the SMs cannot overlap here: the distance kernels fill every
-    SM's register file, so a communication kernel only gets to run between launches.)
-
-    The result buffer is symmetric memory (`torch.distributed._symmetric_memory`), allocated
-    and exchanged once per object and reused by every `run`.  Transports:
+    Transports:
       "multicast"  (default on CUDA when the NVSwitch multicast object is available) the kernel
-                   itself writes its results to the buffer's multicast address with multimem.st,
-                   so the switch delivers every row to all GPUs while the kernel computes: one
-                   kernel does the computation and the exchange, each GPU sends its slab once;
-      "peer_copy"  finished rows are pushed to each peer by copy engines (world - 1 copies of
-                   the slab leave every GPU; at 8 GPUs that takes as long as the computation);
-      "collective" one in-place all-gather after the last launch (also the CPU / Gloo path).
+                   itself writes its results to the result buffer's multicast address with
+                   multimem.st, so the switch delivers every value to all GPUs while the kernel
+                   computes: one kernel does the computation and the exchange, and each GPU sends
+                   its share once.  Because such a store can target any element, the work is not
+                   cut into row slabs here: the 128 x 128 output tiles are dealt out in equal
+                   contiguous runs of the launcher's tile order (`tile_ranges`), which balances
+                   the ranks to within one tile whatever N is.  Two result buffers alternate, so a
+                   run needs a single cross-rank barrier, at its end: the buffer it writes was
+                   last read two runs ago, and every rank has passed a barrier since.
+      "peer_copy"  rank r owns the contiguous slab of rows `shard_rows(N, r, world, 128)`; the
+                   slab is computed in `chunks` launches and finished rows are pushed to each peer
+                   by copy engines while the next launch computes (world - 1 copies of the slab
+                   leave every GPU; at 8 GPUs that takes as long as the computation);
+      "collective" same slabs, one in-place all-gather after the last launch (also the CPU /
+                   Gloo path).  (A collective on the SMs cannot overlap with the computation: the
+                   distance kernels fill every SM's register file.)
+
+    The result buffers are symmetric memory (`torch.distributed._symmetric_memory`), allocated
+    and exchanged once per object and reused by every `run`.
+
+    A sharded result is bit-identical to the single-GPU one for p = 1 and p = 2: every element
+    is the same sequential sum over k wherever its tile runs.  For fractional p it is equal to
+    rounding only when the rows land at different positions of a tile (the two exp2 routes).
+
+    None of the launches checks the device error flag: callers poll
+    `kermac_b200._native.device_error_flag()` on every rank at their own synchronisation points
+    (a bounded wait that ran out leaves the affected tiles unwritten on every rank).
     """
 
     def __init__(self, M: int, N: int, device, group=None, chunks: int = 8, transport: str = "auto"):
@@ -159,11 +204,13 @@ class OverlappedCdist:
         symmetric = device.type == "cuda" and self.world > 1 and transport != "collective"
         shape = (self.world * self.slab_rows, M)
         self._handle, self._peers, self._streams, self._second = None, None, None, None
+        self._buffers, self._handles, self._turn = [], [], 0
         self.launch_count = 0              # distance-kernel launches issued by this object so far
         if symmetric:
             import torch.distributed._symmetric_memory as symm_mem
+            grp = dist_.group.WORLD if group is None else group
             self.full = symm_mem.empty(shape, dtype=torch.float32, device=device)
-            self._handle = symm_mem.rendezvous(self.full, group=dist_.group.WORLD if group is None else group)
+            self._handle = symm_mem.rendezvous(self.full, group=grp)
             has_multicast = bool(getattr(self._handle, "multicast_ptr", 0))
             if transport == "multicast" and not has_multicast:
                 raise RuntimeError("this group has no NVSwitch multicast object for symmetric memory")
@@ -172,12 +219,30 @@ class OverlappedCdist:
             if transport == "peer_copy":
                 self._peers = [self._handle.get_buffer(r, shape, torch.float32) for r in range(self.world)]
                 self._streams = [torch.cuda.Stream(device=device) for _ in range(self.world)]
+            else:
+                second = symm_mem.empty(shape, dtype=torch.float32, device=device)
+                self._buffers = [self.full, second]
+                self._handles = [self._handle, symm_mem.rendezvous(second, group=grp)]
         else:
             if transport in ("multicast", "peer_copy") and self.world > 1:
                 raise RuntimeError(f"transport {transport!r} needs CUDA tensors")
             transport = "collective"
             self.full = torch.empty(shape, dtype=torch.float32, device=device)
         self.transport = transport
+        self.partition = "tiles" if transport == "multicast" else "rows"
+        tiles = (-(-M // 128)) * (-(-N // 128))
+        self.tile_first, self.tile_count = tile_ranges(tiles, self.world)[self.rank]
+        self._tiles = tiles
+
+    def work_share(self) -> float:
+        """Fraction of the whole problem's arithmetic this rank performs."""
+        if self.partition == "tiles":
+            return self.tile_count / self._tiles if self._tiles else 0.0
+        return self.rows / self.N if self.N else 0.0
+
+    def release(self):
+        """Drops the result buffers (the object cannot run afterwards)."""
+        self.full, self._buffers, self._handles, self._handle, self._peers = None, [], [], None, None
 
     def chunk_bounds(self):
         """[(row0, row1)] of the launches inside this rank's slab, on 128-row boundaries."""
@@ -187,17 +252,20 @@ class OverlappedCdist:
     def run(self, a: torch.Tensor, b: torch.Tensor, p: float = 2.0, skip_epilogue: bool = False,
             gather: bool = True, compute: Optional[Callable] = None) -> torch.Tensor:
         """a (M, K) and b (N, K) identical on every rank.  Returns the (N, M) result [n][m],
-        complete on every rank when `gather`; otherwise only this rank's rows are valid.
-        The returned tensor aliases the object's buffer: the next `run` overwrites it."""
+        complete on every rank when `gather`; otherwise only this rank's share is valid.
+        The returned tensor aliases one of the object's buffers: with the multicast transport
+        the next-but-one `run` overwrites it, with the others the next one."""
         if a.dim() != 2 or b.dim() != 2 or a.size(0) != self.M or b.size(0) != self.N:
             raise ValueError("operands do not match the shapes this object was built for")
+        if self.full is None:
+            raise RuntimeError("this object's buffers were released")
         if compute is None:
             from .cdist import cdist as _cdist
 
             def compute(a_, b_, out):
                 return _cdist(a_, b_, out=out, p=p, skip_epilogue=skip_epilogue)
-        if gather and self.world > 1 and self.transport == "multicast":
-            return self._run_multicast(a, b, p, skip_epilogue)
+        if self.world > 1 and self.transport == "multicast":
+            return self._run_tiles(a, b, p, skip_epilogue, gather)
         push = gather and self.world > 1 and self.transport == "peer_copy"
         on_cuda = self.full.is_cuda
         main = torch.cuda.current_stream() if on_cuda else None
@@ -243,35 +311,44 @@ class OverlappedCdist:
             gather_rows_inplace(self.full, self.N, self.group)
         return self.full[:self.N]
 
-
-def _overlapped_run_multicast(self, a, b, p, skip_epilogue):
-    """One launch over this rank's slab whose result stores go to the multicast address of the
-    symmetric buffer: every GPU's buffer receives the rows while the kernel runs."""
-    from . import _native
-    from .build_a_kernel import _current_stream_for, _marshal_build
-    from .cdist import descriptor_for
-    self._handle.barrier()              # nobody is still reading the rows about to be overwritten
-    if self.rows > 0:
-        rows = slice(self.start, self.start + self.rows)
-        descriptor, powers = descriptor_for(p, skip_epilogue)
-        args, _, keep = _marshal_build(descriptor, a, b[rows], self.full[rows].t(), powers.get("p"),
-                                       powers.get("inner_p"), None, None, None, None, 0, 0)
-        args.out = self._handle.multicast_ptr + self.start * self.M * 4
-        args.out_multicast = 1
-        _native.launch_build(args, _current_stream_for(a.device))
-        self.launch_count += 1
-        del keep
-    self._handle.barrier()              # every rank's kernel, and with it its multicast stores, is complete
-    return self.full[:self.N]
-
-
-OverlappedCdist._run_multicast = _overlapped_run_multicast
+    def _run_tiles(self, a, b, p, skip_epilogue, gather):
+        """One launch over this rank's run of output tiles of the WHOLE problem.  With `gather`
+        the stores go to the multicast address of the result buffer, so every GPU's buffer
+        receives the tiles while the kernel runs; without it they go to this GPU's buffer only."""
+        from . import _native
+        from .build_a_kernel import _current_stream_for, _marshal_build
+        from .cdist import descriptor_for
+        turn = self._turn
+        buf, handle = self._buffers[turn], self._handles[turn]
+        out = buf[:self.N]
+        if self.tile_count > 0:
+            descriptor, powers = descriptor_for(p, skip_epilogue)
+            args, _, keep = _marshal_build(descriptor, a, b, out.t(), powers.get("p"),
+                                           powers.get("inner_p"), None, None, None, None, 0, 0)
+            if gather:
+                args.out = handle.multicast_ptr
+                args.out_multicast = 1
+            if _native.build_tile_count(args) != self._tiles:
+                raise RuntimeError("the launcher's tile count differs from the one the ranks were dealt")
+            args.tile_first, args.tile_count = self.tile_first, self.tile_count
+            _native.launch_build(args, _current_stream_for(a.device))
+            self.launch_count += 1
+            del keep
+        if gather:
+            handle.barrier()            # every rank's kernel, and with it its multicast stores, is complete
+            self._turn = 1 - turn       # the next run writes the other buffer: no barrier needed before it
+        return out
 
 
 def kernel_matvec_sharded(kernel_descriptor, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
                           group=None, gather: bool = True, compute: Optional[Callable] = None,
                           **hyper) -> torch.Tensor:
-    """Row-sharded `kernel_matvec` for 2-D operands: y (N, O), or this rank's (rows_r, O) slab."""
+    """Row-sharded `kernel_matvec` for 2-D operands: y (N, O), or this rank's (rows_r, O) slab.
+
+    Bit-identical to the single-GPU result as long as the launcher does not split the sum over m
+    (small M, or many row tiles); where it does, the split follows the number of thread blocks,
+    which sharding changes, and the two results agree to rounding (a few 1e-7 of the largest
+    entry).  Pass `split_m` explicitly to pin the grouping."""
     if a.dim() != 2 or b.dim() != 2 or c.dim() != 2:
         raise ValueError("kernel_matvec_sharded takes 2-D a, b and c")
     world = dist_.get_world_size(group) if dist_.is_initialized() else 1
@@ -311,6 +388,10 @@ def cdist_grad_sharded(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, d: tor
     (O, N, M) tensor when `gather` (one all-gather of the slabs, then a concatenation along n),
     else this rank's (O, rows_r, M) slab.  `compute(a, b_rows, c, d_rows, out=...)` defaults to
     `kermac_b200.cdist_grad`.
+
+    Bit-identical to the single-GPU result while the launcher keeps the whole k range in one thread
+    block; once it splits k (few output tiles, long K) the split follows the number of thread
+    blocks, which sharding changes, and the results agree to rounding only.
     """
     if a.dim() != 2 or b.dim() != 2 or c.dim() != 2 or d.dim() != 2:
         raise ValueError("cdist_grad_sharded takes 2-D a, b, c and d")

@@ -140,6 +140,10 @@ def kernel_matvec(
     selects where the coefficient product runs: "tensor" (tcgen05 tensor cores, three tf32
     products per term, fp32-level accuracy), "fp32" (packed FP32 FMAs) or "auto" / None
     (the environment variable KERMAC_B200_CONTRACTION, else the library default: tensor).
+
+    The tensor-core kernel waits on its copies and on the tensor cores with a bound; a wait that
+    runs out leaves the affected rows unwritten and raises a device flag that nothing here reads:
+    poll `kermac_b200._native.device_error_flag()` at your own synchronisation points.
     """
     args, out, keep_alive = _marshal_matvec(kernel_descriptor, a, b, c, out, p, inner_p, outer_p, bandwidth, epsilon,
                                             regularization, regularization_offset_x, regularization_offset_y)

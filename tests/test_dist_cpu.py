@@ -26,6 +26,24 @@ def test_slab_sizes_cover_and_align():
         kdist.slab_sizes(10, 0)
 
 
+def test_tile_ranges_are_balanced_and_cover_the_tile_order():
+    assert kdist.tile_ranges(10, 4) == [(0, 3), (3, 3), (6, 2), (8, 2)]
+    assert kdist.tile_ranges(2, 4) == [(0, 1), (1, 1), (2, 0), (2, 0)]
+    for total, world in [(55225, 8), (55225, 4), (7, 2), (0, 3), (1, 8)]:
+        ranges = kdist.tile_ranges(total, world)
+        counts = [c for _, c in ranges]
+        assert sum(counts) == total and max(counts) - min(counts) <= 1
+        assert all(ranges[r + 1][0] == ranges[r][0] + ranges[r][1] for r in range(world - 1)) and ranges[0][0] == 0
+    with pytest.raises(ValueError):
+        kdist.tile_ranges(4, 0)
+    # the linear tile order visits every tile once: panels of 16 tile columns, row by row inside a panel
+    for tiles_m, tiles_n in [(235, 235), (3, 40), (17, 20), (1, 1), (5, 16)]:
+        seen = {kdist.tile_coords(t, tiles_m, tiles_n) for t in range(tiles_m * tiles_n)}
+        assert seen == {(i, j) for i in range(tiles_m) for j in range(tiles_n)}
+    assert kdist.tile_coords(0, 235, 235) == (0, 0) and kdist.tile_coords(15, 235, 235) == (0, 15)
+    assert kdist.tile_coords(16, 235, 235) == (1, 0) and kdist.tile_coords(16 * 235, 235, 235) == (0, 16)
+
+
 def test_sharded_helpers_without_a_process_group_run_the_whole_problem():
     from oracle import kermac_oracle as ko
     g = torch.Generator().manual_seed(5)
@@ -99,6 +117,17 @@ def _worker(rank, world, port, n_total, results):
         gslab = kdist.cdist_grad_sharded(ga, b, gc, gd, p=1.5, compute=grad_compute, gather=False)
         g0, g1 = kdist.shard_rows(n_total, rank, world, kdist.GRAD_ROW_ALIGN)
         ok = ok and torch.equal(gfull, gref) and torch.equal(gslab, gref[:, g0:g1])
+        # the tile partition of the multicast transport: every rank marks the elements of its run of
+        # tiles; summed over ranks every element of the (N, M) result is covered exactly once
+        m_total = 300
+        tiles_m, tiles_n = -(-m_total // kdist.TILE), -(-n_total // kdist.TILE)
+        first, count = kdist.tile_ranges(tiles_m * tiles_n, world)[rank]
+        cover = torch.zeros(n_total, m_total)
+        for t in range(first, first + count):
+            tm, tn = kdist.tile_coords(t, tiles_m, tiles_n)
+            cover[tn * kdist.TILE:(tn + 1) * kdist.TILE, tm * kdist.TILE:(tm + 1) * kdist.TILE] += 1.0
+        dist.all_reduce(cover)
+        ok = ok and bool((cover == 1.0).all())
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()

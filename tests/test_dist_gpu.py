@@ -24,7 +24,7 @@ def _worker(rank, world, port, results):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         import kermac_b200 as kermac
-        from kermac_b200 import dist as kdist
+        from kermac_b200 import _native, dist as kdist
         g = torch.Generator().manual_seed(5)
         a_store = torch.randn(96, 700, generator=g).cuda()
         b_store = torch.randn(96, 1000, generator=g).cuda()       # 1000 rows: unequal 128-aligned slabs
@@ -38,11 +38,15 @@ def _worker(rank, world, port, results):
             ok = ok and torch.equal(full, single)                 # sharding must not change a single bit
         for transport in ("multicast", "peer_copy", "collective"):
             ov = kdist.OverlappedCdist(700, 1000, torch.device("cuda", rank), chunks=3, transport=transport)
+            ok = ok and ov.partition == ("tiles" if transport == "multicast" else "rows")
             for p in (1.0, 2.0, 1.3):
                 single = torch.empty(1000, 700, device="cuda")
                 kermac.cdist(a, b, out=single.t(), p=p)
-                ok = ok and torch.equal(ov.run(a, b, p=p), single)
-                ok = ok and torch.equal(ov.run(a, b, p=p), single)     # the buffer is reused run after run
+                for _ in range(3):                                     # the buffers are reused run after run
+                    ok = ok and torch.equal(ov.run(a, b, p=p), single)
+                mine = ov.run(a, b, p=p, gather=False)                 # this rank's share only, no exchange
+                ok = ok and bool((mine == single).float().mean() >= 0.3)
+            ok = ok and _native.device_error_flag() == 0
         y = kdist.kernel_matvec_sharded(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=8.0)
         y1 = kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=8.0)[0]
         ok = ok and torch.equal(y, y1)
@@ -60,6 +64,23 @@ def _worker(rank, world, port, results):
             full = kdist.cdist_grad_sharded(ga, b.contiguous(), gc, gd, p=p)
             single = kermac.cdist_grad(ga, b.contiguous(), gc, gd, p=p)[0]
             ok = ok and torch.equal(full, single)
+        # At sizes where the launcher splits the contracted range (k for the gradient, m for the
+        # matvec) the split depends on the number of thread blocks, which sharding changes: the sums
+        # are then grouped differently and agree to rounding, not bit for bit.
+        ga = torch.rand(4096, 512, generator=g).cuda()
+        gb = torch.randn(256, 4096, generator=g).cuda()
+        gc = torch.randn(4, 4096, generator=g).cuda()
+        gd = torch.randn(256, 512, generator=g).cuda()
+        full = kdist.cdist_grad_sharded(ga, gb, gc, gd, p=1.0)
+        single = kermac.cdist_grad(ga, gb, gc, gd, p=1.0)[0]
+        ok = ok and float((full - single).abs().max() / single.abs().max()) < 5e-6
+        am = torch.randn(64, 200_000, generator=g).cuda().t()
+        bm = torch.randn(64, 512, generator=g).cuda().t()
+        cm = torch.randn(16, 200_000, generator=g).cuda()
+        y = kdist.kernel_matvec_sharded(kermac.kernel_descriptor_laplace_l2, am, bm, cm, bandwidth=8.0)
+        y1 = kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, am, bm, cm, bandwidth=8.0)[0]
+        ok = ok and float((y - y1).abs().max() / y1.abs().max()) < 5e-6
+        ok = ok and _native.device_error_flag() == 0
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
