@@ -9,7 +9,11 @@
 //   - differences, weights and channel FMAs run on packed pairs along m;
 //   - the contracted k range can be split over several thread blocks, whose partial
 //     tiles go to caller-provided scratch and are summed in a fixed order by a
-//     second kernel, so results do not depend on scheduling.
+//     second kernel, so results do not depend on scheduling.  The split is chosen so
+//     that the thread blocks fill whole waves of the machine (two blocks per SM);
+//   - blocks that share a tile of the weight matrix a (the n-tiles of one m-column and
+//     k range) are neighbours in launch order, so a is read from DRAM once;
+//   - p = 1.5 takes |x|^(p-1) as one sqrt.approx instead of the lg2 / ex2 pair.
 #include <mutex>
 
 #include "km_common.cuh"
@@ -20,8 +24,18 @@ namespace {
 
 constexpr int G_THREADS = 256;
 constexpr int G_TM      = 64;
-constexpr int G_BK      = 16;
+#ifndef KM_GRAD_BK
+#define KM_GRAD_BK 32
+#endif
+constexpr int G_BK      = KM_GRAD_BK;   // k rows per staged slab (a multiple of 8)
 constexpr int G_STAGES  = 3;
+#ifndef KM_GRAD_UNROLL
+#define KM_GRAD_UNROLL 32
+#endif
+constexpr int G_UNROLL = KM_GRAD_UNROLL;   // k rows of a slab unrolled together
+// Kernel-side norm kinds: the three of the C-ABI plus the square-root form of KM_NORM_P
+// for p - 1 == 0.5, chosen by the launcher when p is a host scalar.
+constexpr int G_NORM_SQRT = 3;
 
 struct GradParams {
     int M, N, O, K, L;
@@ -42,22 +56,26 @@ __device__ __forceinline__ u64 flip_sign2(u64 a, u64 diff) {
     return a ^ (diff & 0x8000000080000000ull);
 }
 
+// Thread blocks resident per SM that every tile shape is compiled for.
+constexpr int grad_min_blocks(int, int) { return 2; }
+
 template <int NORM, int OT, int NT>
-__global__ void __launch_bounds__(G_THREADS, 2) grad_kernel(const __grid_constant__ GradParams p) {
+__global__ void __launch_bounds__(G_THREADS, grad_min_blocks(OT, NT)) grad_kernel(const __grid_constant__ GradParams p) {
     constexpr int TN      = 16 * NT;
     constexpr int PITCH_A = G_TM + 4;
     constexpr int PITCH_B = TN + 4;
     constexpr int PITCH_C = (OT < 4 ? 4 : OT);
     constexpr int STAGE_FLOATS = G_BK * (PITCH_A + PITCH_B + PITCH_C);
-    __shared__ __align__(16) float smem[G_STAGES * STAGE_FLOATS];
+    extern __shared__ __align__(16) float smem[];      // G_STAGES * STAGE_FLOATS floats (grad_smem_bytes)
 
     const int tid = threadIdx.x;
     const int tmi = tid & 15, tni = tid >> 4;
 
+    // n-tiles fastest: the blocks that read the same (k range, m-column) tile of a run together
     int bx          = blockIdx.x;
+    const int tn    = bx % p.tiles_n; bx /= p.tiles_n;
     const int split = bx % p.splits;  bx /= p.splits;
-    const int tm    = bx % p.tiles_m; bx /= p.tiles_m;
-    const int tn    = bx;
+    const int tm    = bx;
     const int oc    = blockIdx.y;
     const int l     = blockIdx.z;
     const int m0 = tm * G_TM, n0 = tn * TN, o0 = oc * OT;
@@ -101,11 +119,15 @@ __global__ void __launch_bounds__(G_THREADS, 2) grad_kernel(const __grid_constan
         float* sc = sb + G_BK * PITCH_B;
         const int k0 = k_begin + kt * G_BK;
         if (p.a_vec) {
-            // 16 k rows x 16 chunks of 4 m
-            const int kk = tid >> 4, t = (tid & 15) << 2, gk = k0 + kk;
-            int valid = min(4, p.M - m0 - t);
-            valid     = (gk < k_end && valid > 0) ? valid : 0;
-            cp_async_16(smem_u32(sa + kk * PITCH_A + t), valid ? A + (long long)gk * p.lda + t : p.A, valid * 4);
+            // G_BK k rows x 16 chunks of 4 m
+#pragma unroll
+            for (int i = 0; i < (G_BK * G_TM / 4) / G_THREADS; ++i) {
+                const int idx = tid + i * G_THREADS;
+                const int kk = idx >> 4, t = (idx & 15) << 2, gk = k0 + kk;
+                int valid = min(4, p.M - m0 - t);
+                valid     = (gk < k_end && valid > 0) ? valid : 0;
+                cp_async_16(smem_u32(sa + kk * PITCH_A + t), valid ? A + (long long)gk * p.lda + t : p.A, valid * 4);
+            }
         } else {
 #pragma unroll
             for (int i = 0; i < (G_BK * G_TM) / G_THREADS; ++i) {
@@ -115,19 +137,33 @@ __global__ void __launch_bounds__(G_THREADS, 2) grad_kernel(const __grid_constan
                 cp_async_4(smem_u32(sa + kk * PITCH_A + t), ok ? A + (long long)gk * p.lda + t : p.A, ok ? 4 : 0);
             }
         }
+        // b and c are k-contiguous in global memory and staged k-major.  A warp copies 8
+        // consecutive k of 4 rows: 32-byte runs on the global side, and on the shared side
+        // banks 4 kk + t (pitches are 4 mod 32 or 20), all different, so the 4-byte writes
+        // do not collide.
+        constexpr int K8 = G_BK / 8;
 #pragma unroll
         for (int i = 0; i < (G_BK * TN + G_THREADS - 1) / G_THREADS; ++i) {
             const int idx = tid + i * G_THREADS;
             if (idx < G_BK * TN) {
-                const int kk = idx & (G_BK - 1), t = idx >> 4, gk = k0 + kk;
+                const int kk = (idx & 7) + ((idx >> 5) % K8) * 8;
+                const int t  = ((idx >> 3) & 3) + (idx / (32 * K8)) * 4;
+                const int gk = k0 + kk;
                 const bool ok = gk < k_end && (n0 + t) < p.N;
                 cp_async_4(smem_u32(sb + kk * PITCH_B + t), ok ? B + (long long)t * p.ldb + gk : p.B, ok ? 4 : 0);
             }
         }
-        if (tid < G_BK * OT) {
-            const int kk = tid & (G_BK - 1), t = tid >> 4, gk = k0 + kk;
-            const bool ok = gk < k_end && (o0 + t) < p.O;
-            cp_async_4(smem_u32(sc + kk * PITCH_C + t), ok ? C + (long long)t * p.ldc + gk : p.C, ok ? 4 : 0);
+        constexpr int C_ROWS = (OT < 4 ? 4 : OT);
+#pragma unroll
+        for (int i = 0; i < (G_BK * C_ROWS + G_THREADS - 1) / G_THREADS; ++i) {
+            const int idx = tid + i * G_THREADS;
+            if (idx < G_BK * C_ROWS) {
+                const int kk = (idx & 7) + ((idx >> 5) % K8) * 8;
+                const int t  = ((idx >> 3) & 3) + (idx / (32 * K8)) * 4;
+                const int gk = k0 + kk;
+                const bool ok = gk < k_end && (o0 + t) < p.O;
+                if (t < OT) cp_async_4(smem_u32(sc + kk * PITCH_C + t), ok ? C + (long long)t * p.ldc + gk : p.C, ok ? 4 : 0);
+            }
         }
     };
 
@@ -170,6 +206,11 @@ __global__ void __launch_bounds__(G_THREADS, 2) grad_kernel(const __grid_constan
                     w = flip_sign2(av[h], diff);
                 } else if constexpr (NORM == KM_NORM_L2) {
                     w = mul2(av[h], diff);
+                } else if constexpr (NORM == G_NORM_SQRT) {
+                    // |x|^(1/2) sign(x): one MUFU operation per element instead of two
+                    float d0, d1;
+                    unpack2(diff, d0, d1);
+                    w = flip_sign2(mul2(av[h], pack2(sqrt_approx(fabsf(d0)), sqrt_approx(fabsf(d1)))), diff);
                 } else {
                     float d0, d1;
                     unpack2(diff, d0, d1);
@@ -190,6 +231,11 @@ __global__ void __launch_bounds__(G_THREADS, 2) grad_kernel(const __grid_constan
                     }
                 }
 #pragma unroll
+                // A packed FMA whose three sources are three different register pairs (coefficient,
+                // weight, accumulator) holds the FP32 pipe for about three cycles instead of two, which
+                // is what bounds this loop (32 of them and 8 packed subtracts per k row: ~112 cycles for
+                // 80 cycles of arithmetic).  Scalar FMAs (two per pair) and a half packed / half scalar
+                // mix both measured slower: 7.5 and 7.0 ms against 6.6.
                 for (int o = 0; o < OT; ++o) acc[j][o][h] = fma2(cd[o], w, acc[j][o][h]);
             }
         }
@@ -211,7 +257,10 @@ __global__ void __launch_bounds__(G_THREADS, 2) grad_kernel(const __grid_constan
         const float* sc = sb + G_BK * PITCH_B;
         const int kvalid = k_end - (k_begin + kt * G_BK);
         if (kvalid >= G_BK) {
-#pragma unroll
+            // The whole 32-row slab unrolled measured fastest (6.45 ms against 6.58 with 16-row slabs
+            // and 6.65 with an unroll of 8 at K = 30000, M = 4096, N = 256, O = 4); the handful of
+            // registers that spill are reloaded about four times per slab, not per k row.
+#pragma unroll G_UNROLL
             for (int kk = 0; kk < G_BK; ++kk) step(sa, sb, sc, kk);
         } else {
 #pragma unroll 1
@@ -263,14 +312,23 @@ __global__ void __launch_bounds__(256) grad_reduce_kernel(const float* __restric
 
 typedef void (*GradFn)(const GradParams);
 
+struct GradChoice {
+    GradFn fn;
+    int    smem_bytes;
+};
+
+constexpr int grad_smem_bytes(int ot, int nt) {
+    return G_STAGES * G_BK * ((G_TM + 4) + (16 * nt + 4) + (ot < 4 ? 4 : ot)) * 4;
+}
+
 template <int NORM>
-GradFn grad_fn_for(int ot) {
+GradChoice grad_fn_for(int ot) {
     switch (ot) {
-        case 1: return grad_kernel<NORM, 1, 4>;
-        case 2: return grad_kernel<NORM, 2, 4>;
-        case 4: return grad_kernel<NORM, 4, 4>;
-        case 8: return grad_kernel<NORM, 8, 2>;
-        default: return grad_kernel<NORM, 16, 1>;
+        case 1: return {grad_kernel<NORM, 1, 4>, grad_smem_bytes(1, 4)};
+        case 2: return {grad_kernel<NORM, 2, 4>, grad_smem_bytes(2, 4)};
+        case 4: return {grad_kernel<NORM, 4, 4>, grad_smem_bytes(4, 4)};
+        case 8: return {grad_kernel<NORM, 8, 2>, grad_smem_bytes(8, 2)};
+        default: return {grad_kernel<NORM, 16, 1>, grad_smem_bytes(16, 1)};
     }
 }
 int nt_for(int ot) { return ot <= 4 ? 4 : (ot == 8 ? 2 : 1); }
@@ -320,17 +378,25 @@ int make_grad_plan(const KmGradArgs* a, GradPlan* plan) {
     if ((long long)p.tiles_m * p.tiles_n > (1LL << 26)) return fail(KM_ERR_TOO_LARGE, "too many output tiles");
     if (p.o_chunks > 65535) return fail(KM_ERR_TOO_LARGE, "too many output channels");
 
-    // Preferred k split: enough thread blocks for ~2 waves of 2 blocks per SM, at
-    // least 8 slabs of k per block.
+    // Preferred k split.  Thread blocks run two per SM, in waves of `slots`; a launch of `blocks`
+    // blocks takes ceil(blocks / slots) waves however full the last one is.  Among the splits the
+    // k range allows (at least 8 slabs of k per block, at most 64 splits) take the smallest one
+    // whose waves are within 2 % of the best filled; a launch that already fills its waves to 90 %
+    // is left alone (every split costs a partial result written and read back).
     const long long blocks = (long long)p.tiles_m * p.tiles_n * p.o_chunks * p.L;
-    const long long target = 4LL * sm_count();
+    const long long slots  = (long long)grad_min_blocks(plan->ot, plan->nt) * sm_count();
+    auto fill = [&](long long s) {
+        const long long b = blocks * s;
+        return (double)b / (double)(ceil_div_ll(b, slots) * slots);
+    };
     int want = 1;
-    if (blocks < target) {
-        want = (int)ceil_div_ll(target, blocks > 0 ? blocks : 1);
-        const int max_by_k = (int)(p.K / (8 * G_BK));
-        if (want > max_by_k) want = max_by_k;
-        if (want > 64) want = 64;
-        if (want < 1) want = 1;
+    if (blocks > 0 && fill(1) < 0.90) {
+        int max_s = (int)(p.K / (8 * G_BK));
+        if (max_s > 64) max_s = 64;
+        double best = fill(1);
+        for (int s = 2; s <= max_s; ++s) best = fill(s) > best ? fill(s) : best;
+        for (int s = 1; s <= max_s; ++s)
+            if (fill(s) >= best - 0.02) { want = s; break; }
     }
     plan->splits_wanted = want;
     plan->partial_elems = (long long)p.L * p.O * p.N * p.M;
@@ -383,14 +449,23 @@ extern "C" int kermac_b200_cdist_grad(const KmGradArgs* args, void* stream) {
         p.split_stride = 0;
         p.e_vec = aligned16(p.E) && p.e_sn % 4 == 0 && p.e_so % 4 == 0 && p.e_sl % 4 == 0;
     }
-    GradFn fn = nullptr;
+    GradChoice choice = {nullptr, 0};
     switch (args->norm_type) {
-        case KM_NORM_L1: fn = grad_fn_for<KM_NORM_L1>(plan.ot); break;
-        case KM_NORM_L2: fn = grad_fn_for<KM_NORM_L2>(plan.ot); break;
-        default: fn = grad_fn_for<KM_NORM_P>(plan.ot); break;
+        case KM_NORM_L1: choice = grad_fn_for<KM_NORM_L1>(plan.ot); break;
+        case KM_NORM_L2: choice = grad_fn_for<KM_NORM_L2>(plan.ot); break;
+        default:
+            // a host scalar p = 1.5 means |x|^(1/2): the square-root kernel; a device vector of p is
+            // only known to the kernel, which then takes the general lg2 / ex2 route
+            choice = (!args->p.ptr && args->p.value == 1.5f) ? grad_fn_for<G_NORM_SQRT>(plan.ot)
+                                                             : grad_fn_for<KM_NORM_P>(plan.ot);
+            break;
     }
+    GradFn fn = choice.fn;
+    if (int rc = cuda_status(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, choice.smem_bytes),
+                             "cudaFuncSetAttribute(grad_kernel)"))
+        return rc;
     dim3 grid((unsigned)((long long)p.tiles_m * p.tiles_n * splits), (unsigned)p.o_chunks, (unsigned)p.L);
-    fn<<<grid, G_THREADS, 0, st>>>(p);
+    fn<<<grid, G_THREADS, choice.smem_bytes, st>>>(p);
     if (int rc = cuda_status(cudaGetLastError(), "launch of grad_kernel")) return rc;
     if (splits > 1) {
         const long long total = plan.partial_elems;

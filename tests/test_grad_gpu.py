@@ -136,3 +136,41 @@ def test_gradient_configuration_shape_sampled():
         got = kermac.cdist_grad(a.cuda(), b.cuda(), c.cuda(), d.cuda(), p=p)[0]
         ref = ko.cdist_grad_ref(a, b[rows], c, d[rows], p=p, n_chunk=1)[0]
         assert ko.rel_err_signed(got[:, rows], ref) < TOL
+
+
+def test_square_root_route_and_general_route_agree_for_p_one_and_a_half():
+    # a host scalar p = 1.5 takes |x|^(1/2) as one sqrt.approx; the same p as a device tensor is only
+    # known to the kernel and takes lg2 / ex2: both within tolerance of the oracle, ties included
+    K, M, N, O = 300, 200, 48, 4
+    a, b, c, d = gen((K, M), 31, "rand"), gen((N, K), 32), gen((O, K), 33), gen((N, M), 34)
+    d[3, :17] = b[3, 5]                                  # exact ties: |0|^(1/2) = 0 on both routes
+    ref = ko.cdist_grad_ref(a, b, c, d, p=1.5)
+    fast = kermac.cdist_grad(a.cuda(), b.cuda(), c.cuda(), d.cuda(), p=1.5)
+    general = kermac.cdist_grad(a.cuda(), b.cuda(), c.cuda(), d.cuda(), p=torch.tensor([1.5], device="cuda"))
+    assert ko.rel_err_signed(fast, ref) < TOL
+    assert ko.rel_err_signed(general, ref) < TOL
+    assert torch.isfinite(fast).all() and torch.isfinite(general).all()
+
+
+@pytest.mark.parametrize("shape", [(30000, 4096, 256, 4), (4000, 64, 64, 4), (9000, 300, 130, 16), (5000, 128, 64, 1)])
+def test_wave_filling_split_matches_single_pass(shape):
+    # the launcher picks the k split that fills whole waves of thread blocks; whatever it picks, the
+    # result equals the single-pass one to rounding and the oracle on sampled rows
+    K, M, N, O = shape
+    a, b, c, d = gen((K, M), 41, "rand").cuda(), gen((N, K), 42).cuda(), gen((O, K), 43).cuda(), gen((N, M), 44).cuda()
+    auto = kermac.cdist_grad(a, b, c, d, p=1.0)[0]
+    single = torch.empty(O, N, M, device="cuda")
+    g = _native.KmGradArgs()
+    g.m, g.n, g.o, g.k, g.l = M, N, O, K, 1
+    g.a, g.lda = a.data_ptr(), a.stride(0)
+    g.b, g.ldb = b.data_ptr(), b.stride(0)
+    g.c, g.ldc = c.data_ptr(), c.stride(0)
+    g.d, g.ldd = d.data_ptr(), d.stride(0)
+    g.out, g.out_stride_n, g.out_stride_o = single.data_ptr(), single.stride(1), single.stride(0)
+    g.norm_type, g.split_k = _native.NORM_L1, 1
+    _native.launch_grad(g, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert float((auto - single).abs().max() / single.abs().max()) < 5e-6
+    rows = torch.tensor([0, N // 2, N - 1])
+    ref = ko.cdist_grad_ref(a.cpu(), b.cpu()[rows], c.cpu(), d.cpu()[rows], p=1.0)[0]
+    assert ko.rel_err_signed(auto[:, rows.cuda()], ref) < TOL

@@ -85,3 +85,25 @@ def test_static_scratch_rejects_what_does_not_fit_and_single_pass_always_fits():
     _native.launch_grad_static(one, stream)
     torch.cuda.synchronize()
     assert ko.rel_err_signed(out, ko.cdist_grad_ref(a.cpu(), b.cpu(), c.cpu(), d.cpu(), p=2.0)[0]) < TOL
+
+
+def test_automatic_split_is_reduced_to_what_the_array_holds():
+    # split_k = 0 on a problem whose preferred split needs more than the built-in array: the ordinary
+    # entry point falls back when the caller's scratch is too small, and this one does the same
+    # instead of refusing (an explicit split_k that does not fit is still refused)
+    lib = _native.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    K, M, N, O = 3000, 4096, 320, 4                          # one partial result is 21 MB; 9 are preferred
+    a, b, c, d = _inputs(404, K, M, N, O)
+    out = torch.full((O, N, M), float("nan"), device="cuda")
+    g = _args(a, b, c, d, out, _native.NORM_L1, 1.0, 0)
+    wanted = lib.kermac_b200_cdist_grad_scratch_bytes(ctypes.byref(g))
+    assert wanted > _native.GRAD_STATIC_SCRATCH_BYTES, "the case must prefer a split that does not fit"
+    _native.launch_grad_static(g, stream)
+    torch.cuda.synchronize()
+    rows = torch.tensor([0, 159, 319])
+    ref = ko.cdist_grad_ref(a.cpu(), b.cpu()[rows], c.cpu(), d.cpu()[rows], p=1.0)[0]
+    assert ko.rel_err_signed(out[:, rows.cuda()], ref) < TOL
+    explicit = _args(a, b, c, d, out, _native.NORM_L1, 1.0, 4)
+    rc = lib.kermac_b200_cdist_grad_static(ctypes.byref(explicit), ctypes.c_void_p(stream))
+    assert rc == -6 and "built-in array" in _native.last_error()
