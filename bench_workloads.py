@@ -277,6 +277,13 @@ def grad(args, ctx):
         # sub + O fma lane-operations per (m, n, k); the sign flip is a bit operation on the ALU pipe
         "roofline": _fp32_roofline((1.0 + O) * triples, ms1 * 1e-3, pipes, "1 + O lane-operations per (m, n, k) for p = 1"),
     }
+    # what the k step's instruction mix sustains from registers alone (no loads, staging or barriers):
+    # its packed FMAs read three different register pairs and do not issue at the packed rate
+    step_packed = _native.measure_pipe(6, 2048)[0]
+    step_scalar = _native.measure_pipe(7, 2048)[0]
+    line["roofline"]["inner_step_ceiling_lane_ops"] = step_packed
+    line["roofline"]["frac_of_inner_step_ceiling"] = (1.0 + O) * triples / (ms1 * 1e-3) / step_packed
+    line["roofline"]["inner_step_ceiling_scalar_fma_lane_ops"] = step_scalar
     if not args.no_ref_gpu:
         from baseline import ref_kernels
         if ref_kernels.available():
@@ -479,7 +486,7 @@ def verify_sharded(ctx, cyc, a, b):
         full = kdist.cdist_grad_sharded(ga, gb, gc, gd, p=p)
         single = kermac.cdist_grad(ga, gb, gc, gd, p=p)[0]
         err = float((full - single).abs().max()) / float(single.abs().max())
-        ok = err <= 5e-6       # the automatic k split may differ between the sharded and the whole problem
+        ok = err <= 2e-5       # the automatic k split may differ between the sharded and the whole problem
         report[f"cdist_grad p={p:g}"] = {"max_abs_diff_over_max": err, "ok": ok}
         ok_all = ok_all and ok
     flag_clear = _native.device_error_flag() == 0
@@ -496,7 +503,9 @@ def verify_matvec(ctx, y_full, a, b, c, sigma):
     b_rows = b[rows]
     single = kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a, b_rows, c, bandwidth=sigma)[0]
     err = float((y_full[rows] - single).abs().max()) / float(single.abs().max())
-    ok = err <= 5e-6           # the automatic split over m depends on the number of row tiles
+    # the automatic split over m depends on the number of row tiles: sums of 10^6 fp32 terms grouped
+    # differently agree to a few 1e-6 of the largest entry (the oracle tolerance of the tests is 5e-5)
+    ok = err <= 2e-5
     flag_clear = _native.device_error_flag() == 0
     return {"rows_sampled": int(rows.numel()), "max_abs_diff_over_max": err,
             "ok": ctx.all_ranks_ok(ok and flag_clear)}

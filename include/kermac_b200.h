@@ -249,6 +249,10 @@ int kermac_b200_describe_variant(const KmBuildArgs* args, char* buf, int32_t buf
  *   kind 4: the cdist p=2 inner loop (shared-memory operand loads, duplicate moves, packed
  *           sub + fma) with no global staging -> FP32 lane-operations per second
  *   kind 5: the same for the p=1 inner loop (packed sub + add|.|)
+ *   kind 6: the gradient's k step for p = 1 and four channels in registers only (packed subtract,
+ *           sign flip, four packed FMAs with three different register-pair sources per (m, n) pair)
+ *           -> FP32 lane-operations per second (1 + 4 per (m, n, k))
+ *   kind 7: the same with the channel FMAs as scalar instructions
  * Synchronises the device.  Returns 0 and stores the rate in *ops_per_second.
  */
 int kermac_b200_measure_pipe(int32_t kind, int32_t iterations, double* ops_per_second, double* milliseconds);

@@ -375,10 +375,20 @@ __device__ __forceinline__ void consume_slab(u64 (&acc)[8][4], const float* sa, 
     auto step = [&](int kk) {
         const ulonglong2 a0 = *reinterpret_cast<const ulonglong2*>(sa + kk * PITCH);
         const ulonglong2 a1 = *reinterpret_cast<const ulonglong2*>(sa + kk * PITCH + 32);
-        const float4     b0 = *reinterpret_cast<const float4*>(sb + kk * PITCH);
-        const float4     b1 = *reinterpret_cast<const float4*>(sb + kk * PITCH + 16);
         const u64   ap[4] = {a0.x, a0.y, a1.x, a1.y};
-        const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        float bv[8];
+        if constexpr (INNER == IN_DIFF_ABS || INNER == IN_DOT_ABS) {
+            // The |.| step reads the n-side values one by one (warp-wide broadcasts): each lands in the
+            // low half of the register pair it is duplicated into, which measured 0.8 % faster here
+            // (59.6 against 60.1 ms at 30000 x 30000 x 1024); the other steps measured no difference.
+#pragma unroll
+            for (int n = 0; n < 8; ++n) bv[n] = sb[kk * PITCH + (n >> 2) * 16 + (n & 3)];
+        } else {
+            const float4 b0 = *reinterpret_cast<const float4*>(sb + kk * PITCH);
+            const float4 b1 = *reinterpret_cast<const float4*>(sb + kk * PITCH + 16);
+            bv[0] = b0.x; bv[1] = b0.y; bv[2] = b0.z; bv[3] = b0.w;
+            bv[4] = b1.x; bv[5] = b1.y; bv[6] = b1.z; bv[7] = b1.w;
+        }
         inner_block<INNER>(acc, ap, bv, p_inner, sgn);
     };
     // The whole slab is unrolled, so operand loads are scheduled ahead of the math across all

@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(256, 2) inner_loop_kernel(float* sink, int sla
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[j][i] = 0ull;
     for (int s = 0; s < slabs; ++s) {
-        // alternate the start row (0 or 4; rows shift .. shift + 11 stay inside the 16-row
+        // alternate the start row (0 or 4; rows shift .. shift + BK - 5 stay inside the BK-row
         // slab) so the loads are not loop invariant
         const int shift = (s & 1) * 4;
         consume_slab<INNER, BK - 4, PITCH>(acc, pa + shift * PITCH, pb + shift * PITCH, BK, 1.3f, 1.0f);
@@ -91,6 +91,75 @@ __global__ void __launch_bounds__(256, 2) inner_loop_kernel(float* sink, int sla
     if (t == 123.456f) sink[0] = t;
 }
 
+// The gradient's k step for a 4 (m) x 4 (n) x 4 (channel) thread block in registers only:
+// per (n, m-pair) one packed subtract, the sign flip (two bit operations) and four channel
+// FMAs whose three sources are three different registers (coefficient, weight, accumulator).
+// PACKED: the FMAs as fma.rn.f32x2 on register pairs; otherwise as two scalar FMAs each.
+// Nothing is loop invariant (the n-side operand changes every step), so the count of
+// instructions per step is the kernel's, without loads, staging or barriers.
+template <bool PACKED>
+__global__ void __launch_bounds__(256, 2) grad_step_kernel(float* sink, int steps, float seed) {
+    u64   dv[4][2], av[2], acc[4][4][2];
+    float cv[4], bv[4], accs[4][4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        bv[j] = seed * (j + 1) + threadIdx.x;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) dv[j][h] = pack2(seed + j + 0.25f * h, seed - j + 0.5f * threadIdx.x);
+#pragma unroll
+        for (int o = 0; o < 4; ++o) {
+            acc[j][o][0] = acc[j][o][1] = 0ull;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) accs[j][o][e] = 0.0f;
+        }
+    }
+    av[0] = pack2(seed, seed + 1.0f);
+    av[1] = pack2(seed + 2.0f, seed + 3.0f);
+#pragma unroll
+    for (int o = 0; o < 4; ++o) cv[o] = 0.5f + o + 1e-3f * threadIdx.x;
+    for (int it = 0; it < steps; ++it) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            u64 cd[4];
+#pragma unroll
+            for (int o = 0; o < 4; ++o) cd[o] = pack2(cv[o], cv[o]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                bv[j]        = __int_as_float(__float_as_int(bv[j]) ^ (it + r));   // stands in for the operand load
+                const u64 bd = pack2(bv[j], bv[j]);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const u64 diff = sub2(dv[j][h], bd);
+                    const u64 w    = av[h] ^ (diff & 0x8000000080000000ull);
+                    if constexpr (PACKED) {
+#pragma unroll
+                        for (int o = 0; o < 4; ++o) acc[j][o][h] = fma2(cd[o], w, acc[j][o][h]);
+                    } else {
+                        float w0, w1;
+                        unpack2(w, w0, w1);
+#pragma unroll
+                        for (int o = 0; o < 4; ++o) {
+                            accs[j][o][2 * h]     = fmaf(cv[o], w0, accs[j][o][2 * h]);
+                            accs[j][o][2 * h + 1] = fmaf(cv[o], w1, accs[j][o][2 * h + 1]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    float t = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int o = 0; o < 4; ++o) {
+            float a0, a1, a2, a3;
+            unpack2(acc[j][o][0], a0, a1);
+            unpack2(acc[j][o][1], a2, a3);
+            t += a0 + a1 + a2 + a3 + accs[j][o][0] + accs[j][o][1] + accs[j][o][2] + accs[j][o][3];
+        }
+    if (t == 123.456f) sink[0] = t;
+}
+
 typedef void (*PipeFn)(float*, int, float);
 
 }  // namespace
@@ -100,11 +169,12 @@ extern "C" int kermac_b200_measure_pipe(int32_t kind, int32_t iterations, double
                                         double* milliseconds) {
     using namespace km;
     if (!ops_per_second) return fail(KM_ERR_NULL_POINTER, "ops_per_second is NULL");
-    if (kind < 0 || kind > 5) return fail(KM_ERR_BAD_ENUM, "kind %d is not a pipe benchmark", kind);
+    if (kind < 0 || kind > 7) return fail(KM_ERR_BAD_ENUM, "kind %d is not a pipe benchmark", kind);
     if (iterations < 1 || iterations > (1 << 24)) return fail(KM_ERR_BAD_SHAPE, "iterations out of range");
     if (int rc = require_sm100()) return rc;
-    PipeFn fns[6] = {pipe_kernel<0>, pipe_kernel<1>, pipe_kernel<2>, pipe_kernel<3>,
-                     inner_loop_kernel<IN_DIFF_SQUARE>, inner_loop_kernel<IN_DIFF_ABS>};
+    PipeFn fns[8] = {pipe_kernel<0>, pipe_kernel<1>, pipe_kernel<2>, pipe_kernel<3>,
+                     inner_loop_kernel<IN_DIFF_SQUARE>, inner_loop_kernel<IN_DIFF_ABS>,
+                     grad_step_kernel<true>, grad_step_kernel<false>};
     float* sink   = nullptr;
     if (int rc = cuda_status(cudaMalloc(&sink, 256), "cudaMalloc")) return rc;
     const int blocks = sm_count() * (kind >= 4 ? 2 : 8);
@@ -125,8 +195,10 @@ extern "C" int kermac_b200_measure_pipe(int32_t kind, int32_t iterations, double
     // lane-operations per inner statement: fma = 1 (x2 when packed), MUFU pair = 2, sub+add = 2
     const double per_stmt = (kind == 1) ? 2.0 : (kind == 0 ? 1.0 : 2.0);
     double total          = per_stmt * 8.0 * PEAK_CHAINS * (double)iterations * (double)blocks * PEAK_THREADS;
-    // inner-loop kinds: `iterations` slabs of 12 k rows, 64 element-steps per thread and row, 2 lane-ops each
+    // inner-loop kinds: `iterations` slabs of BK - 4 k rows, 64 element-steps per thread and row, 2 lane-ops each
     if (kind >= 4) total = 2.0 * 64.0 * (BUILD_CPA_BK - 4) * (double)iterations * (double)blocks * PEAK_THREADS;
+    // gradient-step kinds: 4 steps per iteration, 16 (m, n) pairs per thread and step, 1 + 4 lane-ops each
+    if (kind >= 6) total = 4.0 * 16.0 * 5.0 * (double)iterations * (double)blocks * PEAK_THREADS;
     *ops_per_second       = total / (ms * 1e-3);
     if (milliseconds) *milliseconds = ms;
     return 0;

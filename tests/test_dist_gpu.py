@@ -73,13 +73,13 @@ def _worker(rank, world, port, results):
         gd = torch.randn(256, 512, generator=g).cuda()
         full = kdist.cdist_grad_sharded(ga, gb, gc, gd, p=1.0)
         single = kermac.cdist_grad(ga, gb, gc, gd, p=1.0)[0]
-        ok = ok and float((full - single).abs().max() / single.abs().max()) < 5e-6
+        ok = ok and float((full - single).abs().max() / single.abs().max()) < 2e-5
         am = torch.randn(64, 200_000, generator=g).cuda().t()
         bm = torch.randn(64, 512, generator=g).cuda().t()
         cm = torch.randn(16, 200_000, generator=g).cuda()
         y = kdist.kernel_matvec_sharded(kermac.kernel_descriptor_laplace_l2, am, bm, cm, bandwidth=8.0)
         y1 = kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, am, bm, cm, bandwidth=8.0)[0]
-        ok = ok and float((y - y1).abs().max() / y1.abs().max()) < 5e-6
+        ok = ok and float((y - y1).abs().max() / y1.abs().max()) < 2e-5
         ok = ok and _native.device_error_flag() == 0
         results[rank] = bool(ok)
     finally:

@@ -170,7 +170,8 @@ def test_wave_filling_split_matches_single_pass(shape):
     g.norm_type, g.split_k = _native.NORM_L1, 1
     _native.launch_grad(g, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
-    assert float((auto - single).abs().max() / single.abs().max()) < 5e-6
+    # fp32 sums of up to 30000 terms grouped differently: a few 1e-6 of the largest entry apart
+    assert float((auto - single).abs().max() / single.abs().max()) < 2e-5
     rows = torch.tensor([0, N // 2, N - 1])
     ref = ko.cdist_grad_ref(a.cpu(), b.cpu()[rows], c.cpu(), d.cpu()[rows], p=1.0)[0]
     assert ko.rel_err_signed(auto[:, rows.cuda()], ref) < TOL
