@@ -431,7 +431,7 @@ def main():
         line["verified"] = bench_workloads.verify_sharded(ctx, cyc, a, b)
 
     if not args.no_e2e:
-        pipe = HostCdist(M, stop - start, K, device=device, slabs=16)
+        pipe = HostCdist(M, stop - start, K, device=device, slabs=32)
         a_pin = a_store.pin_memory()
         b_pin = b_store[:, start:stop].contiguous().pin_memory()
         out_pin = torch.empty((stop - start, M), dtype=torch.float32).pin_memory()

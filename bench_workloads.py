@@ -258,6 +258,7 @@ def grad(args, ctx):
         t_flush = _timed(flush_only, args.steps, args.warmup, ctx.barrier)
         ms1 = _timed(run(ours(1.0)), args.steps, args.warmup, ctx.barrier) - t_flush
         ms15 = _timed(run(ours(1.5)), args.steps, args.warmup, ctx.barrier) - t_flush
+        ms17 = _timed(run(ours(1.7)), max(2, args.steps // 2), min(args.warmup, 2), ctx.barrier) - t_flush
     triples = float(M) * N * K
     ops = (3.0 + 2.0 * O) * triples
     pipes = _pipes(ctx, _native)
@@ -270,10 +271,16 @@ def grad(args, ctx):
                    "l2": "a 256 MB write between steps flushes the L2; its time is subtracted"},
         "clocks": clocks.summary(), "gpu_launches": 2 * args.steps,
         "p=1.5": {"ms_per_step": ms15, "value": ops / (ms15 * 1e-3),
-                  "roofline": {"bound": "mufu", "achieved": 2.0 * triples / (ms15 * 1e-3) / 1e12, "peak": pipes.mufu / 1e12,
-                               "unit": "T MUFU-op/s", "frac": 2.0 * triples / (ms15 * 1e-3) / pipes.mufu,
-                               "note": "2 MUFU operations per (m, n, k) when both lg2 and ex2 go through MUFU; one pair "
-                                       "in four takes its ex2 on the FP32 pipe", "traffic": None}},
+                  "roofline": {"bound": "mufu", "achieved": triples / (ms15 * 1e-3) / 1e12, "peak": pipes.mufu / 1e12,
+                               "unit": "T MUFU-op/s", "frac": triples / (ms15 * 1e-3) / pipes.mufu,
+                               "fp32_lane_utilisation": (2.0 + O) * triples / (ms15 * 1e-3) / pipes.lane,
+                               "note": "p - 1 = 1/2: |x|^(p-1) is one sqrt.approx, 1 MUFU operation per (m, n, k); "
+                                       "2 + O FP32 lane-operations beside it", "traffic": None}},
+        "p=1.7": {"ms_per_step": ms17, "value": ops / (ms17 * 1e-3),
+                  "roofline": {"bound": "mufu", "achieved": 1.75 * triples / (ms17 * 1e-3) / 1e12, "peak": pipes.mufu / 1e12,
+                               "unit": "T MUFU-op/s", "frac": 1.75 * triples / (ms17 * 1e-3) / pipes.mufu,
+                               "note": "general p: lg2 and ex2 per (m, n, k); one pair in four takes its ex2 on the FP32 "
+                                       "pipe, so 1.75 MUFU operations per (m, n, k)", "traffic": None}},
         # sub + O fma lane-operations per (m, n, k); the sign flip is a bit operation on the ALU pipe
         "roofline": _fp32_roofline((1.0 + O) * triples, ms1 * 1e-3, pipes, "1 + O lane-operations per (m, n, k) for p = 1"),
     }
