@@ -6,9 +6,10 @@
 // Slabs of BK k-rows of both operands are brought in by tiled TMA copies
 // (cp.async.bulk.tensor, no multicast) into a ring of STAGES shared-memory stages;
 // each stage has a "full" mbarrier armed with the slab's byte count and an "empty"
-// mbarrier on which every warp arrives once it has read the slab.  Thread 0 issues
-// the copies LAG slabs behind its own consumption, so there is no block-wide
-// barrier in the main loop.  TMA zero-fills rows and columns outside the tensor,
+// mbarrier on which every warp arrives once it has read the slab.  The arrival that
+// completes a stage's empty phase (exactly one lane sees a pending count of 1) hands
+// the next slab for that stage to the TMA engine on the spot: nobody waits for a stage
+// to be released, and there is no block-wide barrier in the main loop.  TMA zero-fills rows and columns outside the tensor,
 // and the last slab only consumes the k-rows that exist.
 //
 // Every mbarrier wait is bounded: if it runs out, the thread records the fact in a
@@ -36,11 +37,10 @@ constexpr int TMA_TILE    = 128;
 constexpr int TMA_THREADS = 256;
 constexpr int TMA_WARPS   = TMA_THREADS / 32;
 
-template <int INNER, int BK, int STAGES, int LAG, bool SYM>
+template <int INNER, int BK, int STAGES, bool SYM>
 __global__ void __launch_bounds__(TMA_THREADS, 2)
 build_tma_kernel(const __grid_constant__ BuildParams p, const __grid_constant__ CUtensorMap map_a,
                  const __grid_constant__ CUtensorMap map_b) {
-    static_assert(LAG >= 1 && LAG < STAGES, "the refill must trail consumption by fewer slabs than there are stages");
     constexpr int STAGE_FLOATS = 2 * BK * TMA_TILE;
     constexpr int STAGE_BYTES  = STAGE_FLOATS * 4;
     extern __shared__ unsigned char smem_raw[];
@@ -78,9 +78,7 @@ build_tma_kernel(const __grid_constant__ BuildParams p, const __grid_constant__ 
     }
     __syncthreads();
 
-    int issued = 0;   // slabs handed to the TMA engine so far (thread 0 only)
     auto issue = [&](int slab) {
-        issued             = slab + 1;
         const int s        = slab % STAGES;
         const uint32_t dst = smem_base + s * STAGE_BYTES;
         mbar_expect_tx(full_bar(s), STAGE_BYTES);
@@ -107,24 +105,25 @@ build_tma_kernel(const __grid_constant__ BuildParams p, const __grid_constant__ 
         for (int i = 0; i < 4; ++i) acc[j][i] = 0ull;
 
     bool alive = true;
+    int fail_kt = -1;   // first slab whose wait ran out on this thread
 
+    // Refill by the last arriver: every warp arrives on a stage's empty barrier when it has read the
+    // slab, and the one arrival that completes the phase (it sees a pending count of 1) hands the
+    // next slab for that stage to the TMA engine on the spot.  Nobody waits for a stage to be
+    // released, and a stage is refilled the moment it is free.
     for (int kt = 0; kt < ktiles; ++kt) {
         const int s = kt % STAGES;
-        if (tid == 0 && kt >= LAG) {
-            const int done_slab = kt - LAG;
-            const int next_slab = done_slab + STAGES;
-            if (next_slab < ktiles) {
-                if (alive && !mbar_wait_bounded(empty_bar(done_slab % STAGES), (done_slab / STAGES) & 1)) alive = false;
-                if (alive) issue(next_slab);
-            }
-        }
         if (alive && !mbar_wait_bounded(full_bar(s), (kt / STAGES) & 1)) alive = false;
 
         const float* sa = smem + s * STAGE_FLOATS + tm_off;
         const float* sb = smem + s * STAGE_FLOATS + BK * TMA_TILE + tn_off;
         consume_slab<INNER, BK, TMA_TILE>(acc, sa, sb, K - kt * BK, p_inner, p.sgn);
         __syncwarp();
-        if (lane == 0) mbar_arrive(empty_bar(s));
+        if (lane == 0 && mbar_arrive_pending(empty_bar(s)) == 1 && kt + STAGES < ktiles && alive) {
+            mbar_try_wait(empty_bar(s), (kt / STAGES) & 1);   // completed by this very arrival: the acquire side of the hand-over
+            issue(kt + STAGES);
+        }
+        if (!alive && fail_kt < 0) fail_kt = kt;
     }
 
     if (!alive) {
@@ -132,7 +131,11 @@ build_tma_kernel(const __grid_constant__ BuildParams p, const __grid_constant__ 
         if (tid == 0) {
             // Give copies that were already handed to the TMA engine a bounded chance
             // to land before this block's shared memory is released.
-            for (int slab = issued > STAGES ? issued - STAGES : 0; slab < issued; ++slab)
+            // any warp may have requested the slabs from the failing one on; those that were never
+            // requested simply run the short limit out
+            const int first = fail_kt < 0 ? 0 : fail_kt;
+            const int last  = first + STAGES < ktiles ? first + STAGES : ktiles;
+            for (int slab = first; slab < last; ++slab)
                 for (int i = 0; i < (1 << 16); ++i)
                     if (mbar_try_wait(full_bar(slab % STAGES), (slab / STAGES) & 1)) break;
         }
@@ -190,17 +193,16 @@ bool operand_tma_ok(const float* base, long long s_t, long long s_k, long long s
 
 typedef void (*TmaKernelFn)(const BuildParams, const CUtensorMap, const CUtensorMap);
 
-// Pipeline shape per inner step: k rows per TMA box / stage, ring depth, and how many
-// slabs thread 0's refill of a stage trails its own consumption.  Measured on B200 at
+// Pipeline shape per inner step: k rows per TMA box / stage and ring depth.  Measured on B200 at
 // 30000 x 30000 x 1024: for the square and product steps 32-row slabs (3 stages) run 2 %
-// faster than 16-row slabs (6 stages), 54.6 vs 55.8 ms, because fewer slab boundaries
-// interrupt the load scheduling; the |.| and |.|^p steps are slower with deep slabs.
+// faster than 16-row slabs (6 stages) because fewer slab boundaries interrupt the load
+// scheduling; the |.| and |.|^p steps are slower with deep slabs.  Refill by the last arriver
+// took the square step from 54.9 ms (thread 0 waiting for each stage's release) to 53.6.
 template <int INNER>
 struct TmaShape {
     static constexpr bool deep = (INNER == IN_DIFF_SQUARE || INNER == IN_DOT_NOOP);
     static constexpr int BK     = deep ? 32 : 16;
     static constexpr int STAGES = deep ? 3 : 6;
-    static constexpr int LAG    = deep ? 1 : 2;
     static constexpr int SMEM   = STAGES * 2 * BK * TMA_TILE * 4 + 128;
 };
 
@@ -212,7 +214,7 @@ struct TmaChoice {
 template <int INNER>
 TmaChoice tma_choice() {
     typedef TmaShape<INNER> S;
-    return {build_tma_kernel<INNER, S::BK, S::STAGES, S::LAG, false>, build_tma_kernel<INNER, S::BK, S::STAGES, S::LAG, true>,
+    return {build_tma_kernel<INNER, S::BK, S::STAGES, false>, build_tma_kernel<INNER, S::BK, S::STAGES, true>,
             S::BK, S::SMEM};
 }
 
@@ -243,8 +245,8 @@ bool tma_supported(const BuildParams& p) {
 }
 
 // Measured on B200 at 30000 x 30000 x 1024: the TMA kernel wins for the square and
-// product steps (55.9 vs 57.0 ms); for |.| and |.|^p the cp.async kernel is ahead
-// (61.4 vs 64.2 ms, 403 vs 431 ms), so those keep it.
+// product steps (53.6 vs 57.0 ms); for |.| and |.|^p the cp.async kernel is ahead
+// (59.6 vs 64.2 ms, 331 vs 356 ms), so those keep it.
 bool tma_preferred(const BuildParams& p) {
     return p.K >= 64 && (p.inner_id == IN_DIFF_SQUARE || p.inner_id == IN_DOT_NOOP);
 }

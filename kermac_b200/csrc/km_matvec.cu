@@ -260,8 +260,9 @@ __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__flo
 // Operand staging comes in two forms.  TMA = false: the 2-stage cp.async pipeline of
 // matvec_kernel (any layout).  TMA = true (operands contiguous along m / n, 16-byte
 // aligned): tiled TMA copies (no multicast) into a 2-stage ring with a full and an empty
-// mbarrier per stage, refilled by thread 0 one slab behind its own consumption, so the
-// k loop has no block-wide barrier and no per-thread copy instructions.
+// mbarrier per stage, each stage refilled by the arrival that completes its empty phase, so
+// the k loop has no block-wide barrier, no per-thread copy instructions and no wait for a
+// stage's release.
 template <int INNER, bool AVEC, bool BVEC, bool TMA>
 __global__ void __launch_bounds__(MV_THREADS, 2)
 matvec_tensor_kernel(const __grid_constant__ MatvecParams p, const __grid_constant__ CUtensorMap map_a,
@@ -372,7 +373,7 @@ matvec_tensor_kernel(const __grid_constant__ MatvecParams p, const __grid_consta
     constexpr int STAGE_FLOATS = 2 * MV_BK * PITCH;
     const int la = (p.a_sl == 0) ? 0 : l;   // broadcast operands have a single batch slice in their map
     const int lb = (p.b_sl == 0) ? 0 : l;
-    int issued = 0;                         // slabs handed to the TMA engine so far (thread 0 only)
+    int fail_it = -1;                       // first slab whose wait ran out on this thread
 
     auto stage = [&](int it) {
         const int chunk = it / ktiles, kt = it - chunk * ktiles;
@@ -381,7 +382,6 @@ matvec_tensor_kernel(const __grid_constant__ MatvecParams p, const __grid_consta
         if constexpr (TMA) {
             const int s        = it % MV_STAGES;
             const uint32_t dst = smem_u32(st);
-            issued             = it + 1;
             mbar_expect_tx(full_bar(s), STAGE_FLOATS * 4);
             tma_load_3d(dst, &map_a, mc0, kt * MV_BK, la, full_bar(s));
             tma_load_3d(dst + MV_BK * PITCH * 4, &map_b, n0, kt * MV_BK, lb, full_bar(s));
@@ -403,13 +403,10 @@ matvec_tensor_kernel(const __grid_constant__ MatvecParams p, const __grid_consta
         const int chunk = it / ktiles, kt = it - chunk * ktiles;
         const int s     = it % MV_STAGES;
         if constexpr (TMA) {
-            // refill the stage of the previous slab once every warp has released it
-            if (tid == 0 && it >= 1 && it - 1 + MV_STAGES < total) {
-                const int done = it - 1;
-                if (!expired && !mbar_wait_bounded(empty_bar(done % MV_STAGES), (done / MV_STAGES) & 1)) expired = true;
-                if (!expired) stage(done + MV_STAGES);
+            if (!expired && !mbar_wait_bounded(full_bar(s), (it / MV_STAGES) & 1)) {
+                expired = true;
+                fail_it = it;
             }
-            if (!expired && !mbar_wait_bounded(full_bar(s), (it / MV_STAGES) & 1)) expired = true;
         } else {
             cp_async_wait<0>();
             __syncthreads();
@@ -421,8 +418,13 @@ matvec_tensor_kernel(const __grid_constant__ MatvecParams p, const __grid_consta
         const float* sb = stages + s * STAGE_FLOATS + MV_BK * PITCH + tn_off;
         consume_slab<INNER, MV_BK, PITCH>(acc, sa, sb, K - kt * MV_BK, p_inner, 1.0f);
         if constexpr (TMA) {
+            // the arrival that completes the stage's empty phase refills it on the spot: nobody
+            // waits for a stage to be released
             __syncwarp();
-            if (lane == 0) mbar_arrive(empty_bar(s));
+            if (lane == 0 && mbar_arrive_pending(empty_bar(s)) == 1 && it + MV_STAGES < total && !expired) {
+                mbar_try_wait(empty_bar(s), (it / MV_STAGES) & 1);   // the acquire side of the hand-over
+                stage(it + MV_STAGES);
+            }
         }
 
         if (kt == ktiles - 1) {
@@ -533,10 +535,15 @@ matvec_tensor_kernel(const __grid_constant__ MatvecParams p, const __grid_consta
         if constexpr (TMA) {
             // give copies already handed to the TMA engine a bounded chance to land before
             // this block's shared memory is released
-            if (tid == 0)
-                for (int slab = issued > MV_STAGES ? issued - MV_STAGES : 0; slab < issued; ++slab)
+            // (any warp may have requested the slabs from the failing one on; those never requested
+            // simply run the short limit out)
+            if (tid == 0) {
+                const int first = fail_it < 0 ? 0 : fail_it;
+                const int last  = first + MV_STAGES < total ? first + MV_STAGES : total;
+                for (int slab = first; slab < last; ++slab)
                     for (int i = 0; i < (1 << 16); ++i)
                         if (mbar_try_wait(full_bar(slab % MV_STAGES), (slab / MV_STAGES) & 1)) break;
+            }
         }
     }
 

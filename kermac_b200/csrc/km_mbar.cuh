@@ -17,6 +17,19 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, int bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrives and returns how many arrivals the current phase was still waiting for BEFORE this
+// one: 1 means this arrival completed the phase (exactly one arriving thread sees 1).
+__device__ __forceinline__ uint32_t mbar_arrive_pending(uint32_t bar) {
+    uint32_t count;
+    asm volatile(
+        "{\n\t.reg .b64 state;\n\t"
+        "mbarrier.arrive.shared::cta.b64 state, [%1];\n\t"
+        "mbarrier.pending_count.b64 %0, state;\n\t}"
+        : "=r"(count)
+        : "r"(bar)
+        : "memory");
+    return count;
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, int parity) {
     uint32_t done;
     asm volatile(
