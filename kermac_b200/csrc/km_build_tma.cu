@@ -197,7 +197,8 @@ typedef void (*TmaKernelFn)(const BuildParams, const CUtensorMap, const CUtensor
 // 30000 x 30000 x 1024: for the square and product steps 32-row slabs (3 stages) run 2 %
 // faster than 16-row slabs (6 stages) because fewer slab boundaries interrupt the load
 // scheduling; the |.| and |.|^p steps are slower with deep slabs.  Refill by the last arriver
-// took the square step from 54.9 ms (thread 0 waiting for each stage's release) to 53.6.
+// took the square step from 54.9 ms (thread 0 waiting for each stage's release) to 53.6; with it
+// 32 x 3 is still the best shape (16 x 6: 56.4, 24 x 4: 54.5, 32 x 2: 54.1, 48 x 2: 54.1 ms).
 template <int INNER>
 struct TmaShape {
     static constexpr bool deep = (INNER == IN_DIFF_SQUARE || INNER == IN_DOT_NOOP);
