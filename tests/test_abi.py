@@ -189,6 +189,9 @@ def test_describe_variant_reports_the_plan():
     col.symmetry = 1
     assert "symmetric=0" in _native.describe_build(col)
     col.symmetry = 0
+    col.out_multicast = 1                          # multicast output: every tile is computed (and sent) by its owner
+    assert "symmetric=0" in _native.describe_build(col)
+    col.out_multicast = 0
     col.tile_first = 1                             # a partial tile range computes every tile it covers
     assert "symmetric=0" in _native.describe_build(col)
     col.tile_first = 0
