@@ -8,7 +8,6 @@ then resolve to kermac_b200's helpers and to the reference's files.  They need t
 package (nvmath-python).  When either is missing the import fails with an ImportError that says
 which; nothing else of `kermac` depends on it.
 """
-import importlib.util
 import os
 
 
@@ -23,10 +22,12 @@ def _source_dir():
 
 
 def _load():
-    if importlib.util.find_spec("nvmath") is None:
+    try:
+        import nvmath  # noqa: F401 - what the reference's linalg imports first
+    except ImportError as exc:
         raise ImportError(
             "kermac.linalg wraps cuSOLVER through the `nvmath` package (nvmath-python), which is not installed; "
-            "the distance operators of kermac do not need it")
+            "the distance operators of kermac do not need it") from exc
     source = _source_dir()
     init = os.path.join(source, "__init__.py") if source else None
     if not init or not os.path.exists(init):

@@ -47,7 +47,11 @@ def test_pre_compile_descriptors_keeps_the_reference_signature():
 
 def test_linalg_import_says_what_is_missing(monkeypatch):
     sys.modules.pop("kermac.linalg", None)
-    have_nvmath = importlib.util.find_spec("nvmath") is not None
+    try:
+        import nvmath  # noqa: F401
+        have_nvmath = True
+    except ImportError:
+        have_nvmath = False
     monkeypatch.delenv("KERMAC_LINALG_PATH", raising=False)
     monkeypatch.delenv("KERMAC_REFERENCE", raising=False)
     with pytest.raises(ImportError) as info:
@@ -92,3 +96,33 @@ def test_wheel_carries_both_packages_and_the_library(tmp_path):
     env["PYTHONPATH"] = str(site)
     run = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=str(tmp_path))
     assert run.returncode == 0 and "ok" in run.stdout, run.stdout + run.stderr
+
+
+def test_linalg_loads_from_an_external_source_directory(monkeypatch, tmp_path):
+    """The mechanism `import kermac.linalg` uses, with stand-ins for what this machine lacks: a fake
+    `nvmath` module and a two-file package that imports the way the reference's linalg does
+    (`import nvmath`, `from ..common import FillMode`, `from .sub import f`, `import kermac`)."""
+    import types
+    src = tmp_path / "linalg_src"
+    src.mkdir()
+    (src / "__init__.py").write_text("from .solver import solve\nall = ['solve']\n")
+    (src / "solver.py").write_text(
+        "import nvmath\nimport kermac\nfrom ..common import FillMode\n"
+        "def solve():\n    return (nvmath.MARK, FillMode.UPPER, kermac.ceil_div(7, 2))\n")
+    fake = types.ModuleType("nvmath")
+    fake.MARK = "fake-nvmath"
+    monkeypatch.setitem(sys.modules, "nvmath", fake)
+    monkeypatch.setenv("KERMAC_LINALG_PATH", str(src))
+    for name in [n for n in sys.modules if n.startswith("kermac.linalg")]:
+        sys.modules.pop(name)
+    try:
+        linalg = importlib.import_module("kermac.linalg")
+        import kermac
+        assert linalg.solve() == ("fake-nvmath", kermac.FillMode.UPPER, 4)
+        assert kermac.linalg is linalg
+        assert importlib.import_module("kermac.linalg.solver").solve is linalg.solve
+    finally:
+        for name in [n for n in sys.modules if n.startswith("kermac.linalg")]:
+            sys.modules.pop(name)
+        import kermac
+        kermac.__dict__.pop("linalg", None)
