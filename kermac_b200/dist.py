@@ -254,7 +254,9 @@ class OverlappedCdist:
         """a (M, K) and b (N, K) identical on every rank.  Returns the (N, M) result [n][m],
         complete on every rank when `gather`; otherwise only this rank's share is valid.
         The returned tensor aliases one of the object's buffers: with the multicast transport
-        the next-but-one `run` overwrites it, with the others the next one."""
+        the next-but-one `run` overwrites it, with the others the next one.  Like a collective,
+        every rank of the group has to make the same sequence of `run` calls with the same
+        `gather` flag: the exchange ends in a cross-rank barrier."""
         if a.dim() != 2 or b.dim() != 2 or a.size(0) != self.M or b.size(0) != self.N:
             raise ValueError("operands do not match the shapes this object was built for")
         if self.full is None:
