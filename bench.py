@@ -431,7 +431,8 @@ def main():
         line["verified"] = bench_workloads.verify_sharded(ctx, cyc, a, b)
 
     if not args.no_e2e:
-        pipe = HostCdist(M, stop - start, K, device=device, slabs=32)
+        # slabs of 5 tile rows: 5 x ceil(M / 128) tiles are a whole number of waves of thread blocks at M = 30000
+        pipe = HostCdist(M, stop - start, K, device=device, slabs=max(1, round((stop - start) / 640)))
         a_pin = a_store.pin_memory()
         b_pin = b_store[:, start:stop].contiguous().pin_memory()
         out_pin = torch.empty((stop - start, M), dtype=torch.float32).pin_memory()

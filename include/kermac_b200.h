@@ -270,6 +270,19 @@ int kermac_b200_device_error_flag(void);
  * (the reference's kernels have no waits on asynchronous units). */
 int kermac_b200_selftest_wait_expiry(int32_t tries, void* stream);
 
+/*
+ * Asynchronous copy of `rows` runs of `row_bytes` bytes between host and device memory, the runs
+ * `src_pitch_bytes` apart in the source and `dst_pitch_bytes` apart in the destination (a strided
+ * 2-D block: cudaMemcpy2DAsync on `stream`).  direction: 0 host -> device, 1 device -> host.  Host
+ * memory should be pinned, otherwise the copy does not overlap with anything.  It lets a caller
+ * whose operands live in host memory send b[K, n0:n1], a column block of the storage layout,
+ * without a staging copy, so the first rows can be computed while the rest of b is still on its way
+ * (kermac_b200.host.HostCdist).  The reference takes device tensors only
+ * (src/kermac/cdist.py:9-83); no reference counterpart.
+ */
+int kermac_b200_copy_2d_async(void* dst, int64_t dst_pitch_bytes, const void* src, int64_t src_pitch_bytes,
+                              int64_t row_bytes, int64_t rows, int32_t direction, void* stream);
+
 const char* kermac_b200_last_error(void);
 int kermac_b200_abi_version(void);
 const char* kermac_b200_build_id(void);

@@ -32,6 +32,7 @@ EXPORTED_SYMBOLS = (
     "kermac_b200_measure_pipe",
     "kermac_b200_device_error_flag",
     "kermac_b200_selftest_wait_expiry",
+    "kermac_b200_copy_2d_async",
     "kermac_b200_last_error",
     "kermac_b200_abi_version",
     "kermac_b200_build_id",
@@ -117,6 +118,9 @@ def _declare(lib: C.CDLL) -> None:
     lib.kermac_b200_build_tile_count.restype = C.c_int64
     lib.kermac_b200_selftest_wait_expiry.argtypes = [C.c_int32, C.c_void_p]
     lib.kermac_b200_selftest_wait_expiry.restype = C.c_int
+    lib.kermac_b200_copy_2d_async.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                              C.c_int32, C.c_void_p]
+    lib.kermac_b200_copy_2d_async.restype = C.c_int
     lib.kermac_b200_cdist_grad.argtypes = [C.POINTER(KmGradArgs), C.c_void_p]
     lib.kermac_b200_cdist_grad.restype = C.c_int
     lib.kermac_b200_cdist_grad_scratch_bytes.argtypes = [C.POINTER(KmGradArgs)]
@@ -215,6 +219,13 @@ def build_tile_count(args: KmBuildArgs) -> int:
 def selftest_wait_expiry(tries: int = 1024, stream_ptr: int = 0) -> None:
     """Launches the one-block kernel whose bounded wait runs out on purpose (see the header)."""
     check(lib().kermac_b200_selftest_wait_expiry(int(tries), C.c_void_p(stream_ptr)), "kermac_b200_selftest_wait_expiry")
+
+
+def copy_2d_async(dst_ptr: int, dst_pitch: int, src_ptr: int, src_pitch: int, row_bytes: int, rows: int,
+                  to_host: bool, stream_ptr: int) -> None:
+    """Strided 2-D copy between host and device memory on a stream (see the header)."""
+    check(lib().kermac_b200_copy_2d_async(C.c_void_p(dst_ptr), dst_pitch, C.c_void_p(src_ptr), src_pitch, row_bytes, rows,
+                                          1 if to_host else 0, C.c_void_p(stream_ptr)), "kermac_b200_copy_2d_async")
 
 
 def launch_grad(args: KmGradArgs, stream_ptr: int) -> None:

@@ -64,6 +64,21 @@ extern "C" {
 
 const char* kermac_b200_last_error(void) { return km::g_last_error; }
 
+int kermac_b200_copy_2d_async(void* dst, int64_t dst_pitch_bytes, const void* src, int64_t src_pitch_bytes,
+                              int64_t row_bytes, int64_t rows, int32_t direction, void* stream) {
+    using namespace km;
+    if (row_bytes < 0 || rows < 0) return fail(KM_ERR_BAD_SHAPE, "row_bytes and rows must be >= 0");
+    if (row_bytes == 0 || rows == 0) return 0;
+    if (!dst || !src) return fail(KM_ERR_NULL_POINTER, "dst and src must not be NULL");
+    if (dst_pitch_bytes < row_bytes || src_pitch_bytes < row_bytes)
+        return fail(KM_ERR_BAD_STRIDE, "a pitch is smaller than the row it spans");
+    if (direction != 0 && direction != 1) return fail(KM_ERR_BAD_ENUM, "direction must be 0 (to device) or 1 (to host)");
+    return cuda_status(cudaMemcpy2DAsync(dst, (size_t)dst_pitch_bytes, src, (size_t)src_pitch_bytes, (size_t)row_bytes,
+                                         (size_t)rows, direction == 0 ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost,
+                                         static_cast<cudaStream_t>(stream)),
+                       "cudaMemcpy2DAsync");
+}
+
 int kermac_b200_abi_version(void) { return KERMAC_B200_ABI_VERSION; }
 
 #define KM_STR2(x) #x

@@ -265,3 +265,15 @@ def test_kernel_matvec_marshalling(recorder, monkeypatch):
         kermac.kernel_matvec(kermac.kernel_descriptor_laplace_l2, a, b, c, bandwidth=8.0, contraction="bf16")
     with pytest.raises(ValueError, match="'KernelType' is 'None'"):
         kermac.kernel_matvec(kermac.kernel_descriptor_l2_norm, a, b, c, regularization=0.1)
+
+
+def test_host_pipeline_slab_plan_covers_the_rows():
+    from kermac_b200.host import HostCdist
+    assert HostCdist.slab_plan(30000, 8) == [3840] * 7 + [3120]
+    assert HostCdist.slab_plan(30000, 47) == [640] * 46 + [560]
+    assert HostCdist.slab_plan(1100, 5) == [256, 256, 256, 256, 76]
+    assert HostCdist.slab_plan(100, 4) == [100] and HostCdist.slab_plan(0, 3) == []
+    for n, slabs in [(1, 1), (129, 2), (4097, 3), (100000, 16), (30000, 32)]:
+        plan = HostCdist.slab_plan(n, slabs)
+        assert sum(plan) == n and all(s > 0 for s in plan)
+        assert all(s % 128 == 0 for s in plan[:-1])            # every slab but the last starts on a tile boundary

@@ -24,3 +24,31 @@ def test_host_pipeline_matches_oracle_and_reuses_its_buffers(p):
         assert ko.rel_err_nonneg(out, ref) < (1e-5 if p in (1.0, 2.0) else 5e-5)
     with pytest.raises(ValueError):
         pipe.run(a_store[:, :10], b_store, out)
+
+
+def test_unpinned_operands_take_the_contiguous_copy():
+    # pageable host memory: b goes up in one contiguous copy instead of per-slab strided ones; same result
+    K, M, N = 32, 300, 700
+    g = torch.Generator().manual_seed(6)
+    a_store, b_store = torch.randn(K, M, generator=g), torch.randn(K, N, generator=g)
+    out = torch.empty(N, M)
+    HostCdist(M, N, K, slabs=3).run(a_store, b_store, out, p=2.0)
+    assert ko.rel_err_nonneg(out, ko.cdist_ref(a_store.t(), b_store.t(), p=2.0)[0].t()) < 1e-5
+
+
+def test_strided_copy_helper_round_trip():
+    from kermac_b200 import _native
+    src = torch.arange(40 * 100, dtype=torch.float32).reshape(40, 100).pin_memory()
+    dev = torch.zeros(40, 100, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    _native.copy_2d_async(dev.data_ptr() + 4 * 10, 400, src.data_ptr() + 4 * 10, 400, 4 * 25, 40, False, stream)
+    torch.cuda.synchronize()
+    want = torch.zeros(40, 100)
+    want[:, 10:35] = src[:, 10:35]
+    assert torch.equal(dev.cpu(), want)
+    back = torch.zeros(40, 100).pin_memory()
+    _native.copy_2d_async(back.data_ptr() + 4 * 10, 400, dev.data_ptr() + 4 * 10, 400, 4 * 25, 40, True, stream)
+    torch.cuda.synchronize()
+    assert torch.equal(back, want)
+    with pytest.raises(ValueError):
+        _native.copy_2d_async(dev.data_ptr(), 8, src.data_ptr(), 400, 100, 4, False, stream)     # pitch < row
