@@ -24,15 +24,9 @@ namespace {
 
 constexpr int G_THREADS = 256;
 constexpr int G_TM      = 64;
-#ifndef KM_GRAD_BK
-#define KM_GRAD_BK 32
-#endif
-constexpr int G_BK      = KM_GRAD_BK;   // k rows per staged slab (a multiple of 8)
+constexpr int G_BK      = 32;   // k rows per staged slab (a multiple of 8)
 constexpr int G_STAGES  = 3;
-#ifndef KM_GRAD_UNROLL
-#define KM_GRAD_UNROLL 32
-#endif
-constexpr int G_UNROLL = KM_GRAD_UNROLL;   // k rows of a slab unrolled together
+constexpr int G_UNROLL  = 32;   // k rows of a slab unrolled together
 // Kernel-side norm kinds: the three of the C-ABI plus the square-root form of KM_NORM_P
 // for p - 1 == 0.5, chosen by the launcher when p is a host scalar.
 constexpr int G_NORM_SQRT = 3;
