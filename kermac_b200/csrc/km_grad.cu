@@ -189,6 +189,16 @@ __global__ void __launch_bounds__(G_THREADS, grad_min_blocks(OT, NT)) grad_kerne
         u64 cd[OT];
 #pragma unroll
         for (int o = 0; o < OT; ++o) cd[o] = pack2(cv[o], cv[o]);
+        // Order of the 8 (n, m-pair) x OT channel FMAs of a k row.  They all cost the same in theory;
+        // in practice the order decides which source operands repeat from one instruction to the next
+        // and how the compiler lays the registers out, and a few per cent hang on it.  Measured at
+        // K = 30000, M = 4096, N = 256, O = 4 (ms, orders: 0 = weight by weight as it is computed, then
+        // with all weights of the row first, 1 = channel / n / pair, 3 = pair / channel / n):
+        //   p = 1:   0: 6.45   1: 6.24   3: 6.39        p = 2:   0: 6.37   1: 6.25   3: 6.21
+        //   p = 1.5: 0: 8.72   1: 8.82   3: 8.66        p = 1.7: 0: 14.84  1: 15.78  3: 15.06
+        // Other channel tiles measured no difference and keep order 0.
+        constexpr int ORDER = (OT != 4) ? 0 : (NORM == KM_NORM_L1 ? 1 : ((NORM == KM_NORM_L2 || NORM == G_NORM_SQRT) ? 3 : 0));
+        if constexpr (ORDER == 0) {
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
             const u64 bd = pack2(bv[j], bv[j]);
@@ -231,6 +241,62 @@ __global__ void __launch_bounds__(G_THREADS, grad_min_blocks(OT, NT)) grad_kerne
                 // 80 cycles of arithmetic).  Scalar FMAs (two per pair) and a half packed / half scalar
                 // mix both measured slower: 7.5 and 7.0 ms against 6.6.
                 for (int o = 0; o < OT; ++o) acc[j][o][h] = fma2(cd[o], w, acc[j][o][h]);
+            }
+        }
+        } else {
+            u64 wv[NT][2];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const u64 bd = pack2(bv[j], bv[j]);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                const u64 diff = sub2(dv[j][h], bd);
+                u64 w;
+                if constexpr (NORM == KM_NORM_L1) {
+                    w = flip_sign2(av[h], diff);
+                } else if constexpr (NORM == KM_NORM_L2) {
+                    w = mul2(av[h], diff);
+                } else if constexpr (NORM == G_NORM_SQRT) {
+                    // |x|^(1/2) sign(x): one MUFU operation per element instead of two
+                    float d0, d1;
+                    unpack2(diff, d0, d1);
+                    w = flip_sign2(mul2(av[h], pack2(sqrt_approx(fabsf(d0)), sqrt_approx(fabsf(d1)))), diff);
+                } else {
+                    float d0, d1;
+                    unpack2(diff, d0, d1);
+                    if (h == 0 && (j & 1) == 0 && NT > 1) {
+                        // one pair in four takes only lg2 on MUFU and the exponential on the
+                        // FP32 pipe (ex2_poly2); more than that and instruction issue, not MUFU,
+                        // becomes the limit
+                        const u64 x = mul2(pack2(lg2_approx(fabsf(d0)), lg2_approx(fabsf(d1))), pack2(pm1, pm1));
+                        float x0, x1;
+                        unpack2(x, x0, x1);
+                        u64 r, scale;
+                        ex2_poly2(x0, x1, r, scale);
+                        w = mul2(av[h], flip_sign2(mul2(r, scale), diff));
+                    } else {
+                        const float g0 = copysignf(pow_approx(fabsf(d0), pm1), d0);
+                        const float g1 = copysignf(pow_approx(fabsf(d1), pm1), d1);
+                        w              = mul2(av[h], pack2(g0, g1));
+                    }
+                }
+                    wv[j][h] = w;
+                }
+            }
+            if constexpr (ORDER == 1) {
+#pragma unroll
+                for (int o = 0; o < OT; ++o)
+#pragma unroll
+                    for (int j = 0; j < NT; ++j)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) acc[j][o][h] = fma2(cd[o], wv[j][h], acc[j][o][h]);
+            } else {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int o = 0; o < OT; ++o)
+#pragma unroll
+                        for (int j = 0; j < NT; ++j) acc[j][o][h] = fma2(cd[o], wv[j][h], acc[j][o][h]);
             }
         }
     };
