@@ -196,7 +196,9 @@ __global__ void __launch_bounds__(G_THREADS, grad_min_blocks(OT, NT)) grad_kerne
         // with all weights of the row first, 1 = channel / n / pair, 3 = pair / channel / n):
         //   p = 1:   0: 6.45   1: 6.24   3: 6.39        p = 2:   0: 6.37   1: 6.25   3: 6.21
         //   p = 1.5: 0: 8.72   1: 8.82   3: 8.66        p = 1.7: 0: 14.84  1: 15.78  3: 15.06
-        // Other channel tiles measured no difference and keep order 0.
+        // With the two multiplicands exchanged (weight first, coefficient second) order 1 falls back to 6.9 ms:
+        // what pays is the FIRST source repeating over a long run of instructions (the coefficient pair over
+        // all 8 weights of the row).  Other channel tiles measured no difference and keep order 0.
         constexpr int ORDER = (OT != 4) ? 0 : (NORM == KM_NORM_L1 ? 1 : ((NORM == KM_NORM_L2 || NORM == G_NORM_SQRT) ? 3 : 0));
         if constexpr (ORDER == 0) {
 #pragma unroll
