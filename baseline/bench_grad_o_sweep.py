@@ -1,5 +1,6 @@
 """cdist_grad at the gradient benchmark shape (K = 30000 contracted, M = 4096, N = 256, seed 3) for
-O in {1, 2, 4, 8, 16, 32} channels: kermac_b200 next to the reference's own kernel on the same GPU.
+O in {1, 2, 4, 8, 16, 32, 64} channels: kermac_b200 (its FP32 kernel, its tensor-core kernel and what the
+automatic choice takes) next to the reference's own kernel on the same GPU.
 
     python baseline/bench_grad_o_sweep.py
 
@@ -52,13 +53,17 @@ def main():
     b = torch.randn(N, K, generator=g).cuda()
     d = torch.randn(N, M, generator=g).cuda()
     a = torch.rand(M, K, generator=g).t().contiguous().cuda()
-    for O in (1, 2, 4, 8, 16, 32):
+    for O in (1, 2, 4, 8, 16, 32, 64):
         c = torch.randn(O, K, generator=g).cuda()
         out = torch.empty(1, O, N, M, device="cuda")
         o_ref = torch.empty(O, N, M, device="cuda")
         row = {"O": O}
         for p in (1.0, 1.5, 2.0, 1.7):
             row[f"ours_p{p:g}_ms"] = round(timed(lambda: kermac.cdist_grad(a, b, c, d, out=out, p=p)), 3)
+            if O >= 8 and p in (1.0, 1.7):
+                for mode in ("fp32", "tensor"):
+                    t = timed(lambda: kermac.cdist_grad(a, b, c, d, out=out, p=p, contraction=mode), steps=3, warmup=1)
+                    row[f"{mode}_p{p:g}_ms"] = round(t, 3)
             if ref_kernels.available() and p in (1.0, 1.5):
                 ref = timed(lambda: ref_kernels.ref_cdist_grad(a, b, c, d, o_ref, p), steps=3, warmup=1)
                 row[f"ref_p{p:g}_ms"] = round(ref, 3)

@@ -291,6 +291,26 @@ def grad(args, ctx):
     line["roofline"]["inner_step_ceiling_lane_ops"] = step_packed
     line["roofline"]["frac_of_inner_step_ceiling"] = (1.0 + O) * triples / (ms1 * 1e-3) / step_packed
     line["roofline"]["inner_step_ceiling_scalar_fma_lane_ops"] = step_scalar
+    # 32 channels: the tensor-core kernel (the automatic choice from 17 channels on) next to the FP32 kernel.
+    # Its bound is the tensor pipe at the rate narrow MMAs get: a 128 x 8 tf32 MMA of up to 64 output
+    # columns holds the pipe ~45 cycles; two of them (head and remainder of the weights) per 128 pairs x 8 k.
+    O2 = 32
+    c2 = torch.randn(O2, K, generator=g).cuda()
+    out2 = torch.empty(1, O2, N, M, device="cuda")
+    few = max(2, args.steps // 3)
+    t_fp = _timed(run(lambda: kermac.cdist_grad(ad, bd, c2, dd, out=out2, p=1.0, contraction="fp32")), few, 1, ctx.barrier) - t_flush
+    fp_out = out2.clone()
+    t_tc = _timed(run(lambda: kermac.cdist_grad(ad, bd, c2, dd, out=out2, p=1.0, contraction="tensor")), few, 1, ctx.barrier) - t_flush
+    mmas = (float(M) * N / 128.0) * (K / 8.0) * 2.0
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    mma_rate = sms * (line["clocks"].get("sm_mhz") or 1965.0) * 1e6 / 45.0
+    line["O=32"] = {"fp32_kernel_ms": t_fp, "tensor_kernel_ms": t_tc, "ratio": t_fp / t_tc,
+                    "max_abs_diff_over_max": float((out2 - fp_out).abs().max() / fp_out.abs().max()),
+                    "device_error_flag": _native.device_error_flag(),
+                    "roofline": {"bound": "tensor", "achieved": mmas / (t_tc * 1e-3) / 1e9, "peak": mma_rate / 1e9,
+                                 "unit": "G narrow-MMA/s", "frac": mmas / (t_tc * 1e-3) / mma_rate, "traffic": None,
+                                 "note": "tcgen05.mma kind::tf32 128 x N x 8 with N <= 64: ~45 cycles each whatever N "
+                                         "(a quarter of the pipe's rate at N = 32, half at N = 64); 2 per 128 pairs x 8 k"}}
     if not args.no_ref_gpu:
         from baseline import ref_kernels
         if ref_kernels.available():

@@ -42,7 +42,7 @@
 extern "C" {
 #endif
 
-#define KERMAC_B200_ABI_VERSION 5
+#define KERMAC_B200_ABI_VERSION 6
 
 /* Rejected preconditions (negative return codes). */
 #define KM_ERR_NULL_POINTER   (-1)
@@ -149,6 +149,13 @@ int64_t kermac_b200_build_tile_count(const KmBuildArgs* args);
  * `scratch` may be NULL; when given it must hold `scratch_bytes` bytes of device
  * memory, which lets the launcher split the contracted k range over several
  * thread blocks (see kermac_b200_cdist_grad_scratch_bytes).
+ * `contraction` (KM_CONTRACT_*, defined below with kermac_b200_kernel_matvec) selects where the
+ * products with c run: KM_CONTRACT_FP32 as packed FP32 FMAs; KM_CONTRACT_TENSOR on the tcgen05
+ * tensor cores, up to 32 channels at a time, as three tf32 products per term (weights and
+ * coefficients split into a tf32 head and an fp32 remainder, accumulation chains of 128 k added up
+ * in fp32: fp32-level accuracy, not the FP32 kernel's bits); KM_CONTRACT_AUTO takes the tensor
+ * cores from 17 channels and 256 k on.  The weights a * g(d - b) are computed in FP32 either way.  A bounded
+ * wait inside the tensor-core kernel that runs out raises kermac_b200_device_error_flag().
  */
 typedef struct KmGradArgs {
     int32_t m, n, o, k, l;
@@ -161,6 +168,7 @@ typedef struct KmGradArgs {
     KmHyper p;                /* used when norm_type == KM_NORM_P */
     void*   scratch; int64_t scratch_bytes;
     int32_t split_k;          /* 0 = automatic (1 when scratch is NULL) */
+    int32_t contraction;      /* KM_CONTRACT_*: where the channel products run (see below) */
 } KmGradArgs;
 
 int kermac_b200_cdist_grad(const KmGradArgs* args, void* stream);

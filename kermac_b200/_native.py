@@ -11,7 +11,7 @@ import os
 import threading
 from typing import Optional
 
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 # enum values of include/kermac_b200.h
 INNER_DIFF, INNER_DOT = 0, 1
@@ -74,6 +74,7 @@ class KmGradArgs(C.Structure):
         ("p", KmHyper),
         ("scratch", C.c_void_p), ("scratch_bytes", C.c_int64),
         ("split_k", C.c_int32),
+        ("contraction", C.c_int32),
     ]
 
 

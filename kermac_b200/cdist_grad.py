@@ -19,7 +19,12 @@ from .common import merge_batch_size, tensor_stats
 __all__ = ["cdist_grad"]
 
 
-def _marshal_grad(a, b, c, d, out, p):
+_CONTRACTIONS = {"auto": 0, "fp32": 1, "tensor": 2}   # KM_CONTRACT_* of the C-ABI
+
+
+def _marshal_grad(a, b, c, d, out, p, contraction="auto"):
+    if contraction not in _CONTRACTIONS:
+        raise ValueError(f"contraction must be one of {sorted(_CONTRACTIONS)}, got {contraction!r}")
     if not all(isinstance(x, torch.Tensor) for x in (a, b, c, d)):
         raise TypeError("All inputs must be PyTorch tensors")
     if out is not None and not isinstance(out, torch.Tensor):
@@ -114,6 +119,7 @@ def _marshal_grad(a, b, c, d, out, p):
     args.norm_type = norm_type
     args.p = _native.hyper(p if isinstance(p, torch.Tensor) else p_value)
     args.scratch, args.scratch_bytes, args.split_k = None, 0, 0
+    args.contraction = _CONTRACTIONS[contraction]
     return args, out
 
 
@@ -125,6 +131,8 @@ def cdist_grad(
     out: torch.Tensor = None,  # [O, N, M] grad
     p: Union[float, torch.Tensor] = 2.0,
     debug=False,
+    *,
+    contraction: str = "auto",
 ):
     """out[o, n, m] = sum_k c[o, k] * a[k, m] * sign(d[n, m] - b[n, k]) * |d[n, m] - b[n, k]|^(p - 1).
 
@@ -132,11 +140,17 @@ def cdist_grad(
     stride 1 in its last dimension.  sign() is copysign(1, x): an exact tie counts as +1
     for p = 1, as in the reference's kernel (include/p_norm_gradient.cuh:373-394).
 
+    `contraction` (not in the reference) selects where the products with `c` run: "fp32" as
+    packed FP32 FMAs, "tensor" on the tcgen05 tensor cores (three tf32 products per term,
+    fp32-level accuracy), "auto" the tensor cores from 17 channels and 256 k on.  The tensor-core
+    kernel bounds its waits; one that runs out is reported by
+    `kermac_b200._native.device_error_flag()`.
+
     Raises:
         TypeError: inputs are not float32 torch tensors.
         ValueError: shapes, strides, dimensions or CUDA devices are invalid.
     """
-    args, out = _marshal_grad(a, b, c, d, out, p)
+    args, out = _marshal_grad(a, b, c, d, out, p, contraction)
     stream_ptr = _current_stream_for(a.device)
     library = _native.lib()
     import ctypes

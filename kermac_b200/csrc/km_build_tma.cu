@@ -322,6 +322,7 @@ extern "C" int kermac_b200_device_error_flag(void) {
     if (km::cuda_status(cudaMemcpyFromSymbol(&v, km::g_tma_wait_expired, sizeof(int)), "cudaMemcpyFromSymbol")) return KM_ERR_INTERNAL;
     if (v) cudaMemcpyToSymbol(km::g_tma_wait_expired, &zero, sizeof(int));
     const int mv = km::matvec_take_wait_flag();
-    if (mv < 0) return KM_ERR_INTERNAL;
-    return (v || mv) ? 1 : 0;
+    const int gv = km::grad_tensor_take_wait_flag();
+    if (mv < 0 || gv < 0) return KM_ERR_INTERNAL;
+    return (v || mv || gv) ? 1 : 0;
 }

@@ -30,6 +30,9 @@ constexpr int G_UNROLL  = 32;   // k rows of a slab unrolled together
 // Kernel-side norm kinds: the three of the C-ABI plus the square-root form of KM_NORM_P
 // for p - 1 == 0.5, chosen by the launcher when p is a host scalar.
 constexpr int G_NORM_SQRT = 3;
+static_assert(G_NORM_SQRT == GT_NORM_SQRT && G_BK == GT_BK, "the two gradient kernels share the planner");
+// Channels from which KM_CONTRACT_AUTO takes the tensor-core kernel.
+constexpr int KM_GRAD_TENSOR_MIN_O = 17;
 
 struct GradParams {
     int M, N, O, K, L;
@@ -398,6 +401,7 @@ int nt_for(int ot) { return ot <= 4 ? 4 : (ot == 8 ? 2 : 1); }
 struct GradPlan {
     GradParams p;
     int ot, nt;
+    bool tensor;               // channel contraction on the tensor cores (km_grad_tensor.cu)
     int splits_wanted;
     long long partial_elems;   // elements of one dense partial result
 };
@@ -421,6 +425,8 @@ int make_grad_plan(const KmGradArgs* a, GradPlan* plan) {
     if (a->l > 1 && a->out_stride_l == 0) return fail(KM_ERR_BAD_STRIDE, "out cannot be broadcast over the batch");
     if (!hyper_ok(a->p)) return fail(KM_ERR_BAD_HYPERPARAM, "p needs a non-negative batch stride");
     if (a->split_k < 0) return fail(KM_ERR_BAD_SHAPE, "split_k must be >= 0");
+    if (a->contraction < KM_CONTRACT_AUTO || a->contraction > KM_CONTRACT_TENSOR)
+        return fail(KM_ERR_BAD_ENUM, "contraction must be KM_CONTRACT_AUTO, _FP32 or _TENSOR");
 
     GradParams& p = plan->p;
     p.M = a->m; p.N = a->n; p.O = a->o; p.K = a->k; p.L = a->l;
@@ -431,10 +437,17 @@ int make_grad_plan(const KmGradArgs* a, GradPlan* plan) {
     p.p = a->p;
     int ot = 1;
     while (ot < a->o && ot < 16) ot *= 2;
+    // The tensor-core kernel forms each weight once for up to 32 channels and leaves the channel
+    // products to the MMA.  Up to 16 channels the FP32 kernel is level or faster (K = 30000, M = 4096,
+    // N = 256: 20.4 against 22.9 ms at 16); from 17 on it needs a second pass and the tensor cores
+    // win (40.4 against 28.9 ms at 32).  The tensor kernel needs at least one slab of k.
+    plan->tensor = a->k > 0 && (a->contraction == KM_CONTRACT_TENSOR ||
+                                (a->contraction == KM_CONTRACT_AUTO && a->o >= KM_GRAD_TENSOR_MIN_O && a->k >= 8 * G_BK));
+    if (plan->tensor) ot = gt_ot_for(a->o);
     plan->ot = ot;
     plan->nt = nt_for(ot);
-    p.tiles_m  = (int)ceil_div_ll(p.M, G_TM);
-    p.tiles_n  = (int)ceil_div_ll(p.N, 16 * plan->nt);
+    p.tiles_m  = (int)ceil_div_ll(p.M, plan->tensor ? GT_TM : G_TM);
+    p.tiles_n  = (int)ceil_div_ll(p.N, plan->tensor ? gt_tn_for(ot) : 16 * plan->nt);
     p.o_chunks = (int)ceil_div_ll(p.O > 0 ? p.O : 1, ot);
     p.a_vec    = aligned16(p.A) && p.lda % 4 == 0 && p.a_sl % 4 == 0;
     if ((long long)p.tiles_m * p.tiles_n > (1LL << 26)) return fail(KM_ERR_TOO_LARGE, "too many output tiles");
@@ -446,7 +459,7 @@ int make_grad_plan(const KmGradArgs* a, GradPlan* plan) {
     // whose waves are within 2 % of the best filled; a launch that already fills its waves to 90 %
     // is left alone (every split costs a partial result written and read back).
     const long long blocks = (long long)p.tiles_m * p.tiles_n * p.o_chunks * p.L;
-    const long long slots  = (long long)grad_min_blocks(plan->ot, plan->nt) * sm_count();
+    const long long slots  = (long long)(plan->tensor ? gt_blocks_per_sm(plan->ot) : grad_min_blocks(plan->ot, plan->nt)) * sm_count();
     auto fill = [&](long long s) {
         const long long b = blocks * s;
         return (double)b / (double)(ceil_div_ll(b, slots) * slots);
@@ -511,16 +524,30 @@ extern "C" int kermac_b200_cdist_grad(const KmGradArgs* args, void* stream) {
         p.split_stride = 0;
         p.e_vec = aligned16(p.E) && p.e_sn % 4 == 0 && p.e_so % 4 == 0 && p.e_sl % 4 == 0;
     }
+    // a host scalar p = 1.5 means |x|^(1/2): the square-root kernels; a device vector of p is only
+    // known to the kernel, which then takes the general lg2 / ex2 route
+    const bool sqrt_route = (args->norm_type == KM_NORM_P && !args->p.ptr && args->p.value == 1.5f);
+    if (plan.tensor) {
+        GradTensorParams t;
+        t.M = p.M; t.N = p.N; t.O = p.O; t.K = p.K; t.L = p.L;
+        t.A = p.A; t.lda = p.lda; t.a_sl = p.a_sl;
+        t.B = p.B; t.ldb = p.ldb; t.b_sl = p.b_sl;
+        t.C = p.C; t.ldc = p.ldc; t.c_sl = p.c_sl;
+        t.D = p.D; t.ldd = p.ldd; t.d_sl = p.d_sl;
+        t.E = p.E; t.e_sn = p.e_sn; t.e_so = p.e_so; t.e_sl = p.e_sl;
+        t.p = p.p;
+        t.ot = plan.ot;
+        t.rg = gt_rg_for(plan.ot);
+        t.tiles_m = p.tiles_m; t.tiles_n = p.tiles_n; t.o_chunks = p.o_chunks; t.splits = p.splits;
+        t.k_per_split = p.k_per_split; t.split_stride = p.split_stride;
+        t.c_vec = aligned16(p.C) && p.ldc % 4 == 0 && p.c_sl % 4 == 0;
+        if (int rc = grad_tensor_launch(t, sqrt_route ? GT_NORM_SQRT : args->norm_type, st)) return rc;
+    } else {
     GradChoice choice = {nullptr, 0};
     switch (args->norm_type) {
         case KM_NORM_L1: choice = grad_fn_for<KM_NORM_L1>(plan.ot); break;
         case KM_NORM_L2: choice = grad_fn_for<KM_NORM_L2>(plan.ot); break;
-        default:
-            // a host scalar p = 1.5 means |x|^(1/2): the square-root kernel; a device vector of p is
-            // only known to the kernel, which then takes the general lg2 / ex2 route
-            choice = (!args->p.ptr && args->p.value == 1.5f) ? grad_fn_for<G_NORM_SQRT>(plan.ot)
-                                                             : grad_fn_for<KM_NORM_P>(plan.ot);
-            break;
+        default: choice = sqrt_route ? grad_fn_for<G_NORM_SQRT>(plan.ot) : grad_fn_for<KM_NORM_P>(plan.ot); break;
     }
     GradFn fn = choice.fn;
     if (int rc = cuda_status(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, choice.smem_bytes),
@@ -529,6 +556,7 @@ extern "C" int kermac_b200_cdist_grad(const KmGradArgs* args, void* stream) {
     dim3 grid((unsigned)((long long)p.tiles_m * p.tiles_n * splits), (unsigned)p.o_chunks, (unsigned)p.L);
     fn<<<grid, G_THREADS, choice.smem_bytes, st>>>(p);
     if (int rc = cuda_status(cudaGetLastError(), "launch of grad_kernel")) return rc;
+    }
     if (splits > 1) {
         const long long total = plan.partial_elems;
         int blocks = (int)(ceil_div_ll(total, 256) < 4LL * sm_count() ? ceil_div_ll(total, 256) : 4LL * sm_count());

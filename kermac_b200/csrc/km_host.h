@@ -27,6 +27,39 @@ int sm_count();
 // (km_matvec.cu); the device must already be synchronised.  0 / 1, or -1 on error.
 int matvec_take_wait_flag();
 
+// Tensor-core form of the gradient contraction (km_grad_tensor.cu): tile extents the planner
+// needs, the kernel's parameter block and its launcher.  norm_kind is a KmNormType or
+// GT_NORM_SQRT (|x|^(1/2), chosen by the caller for a host scalar p = 1.5).
+constexpr int GT_TM = 32;          // m per thread block
+constexpr int GT_BK = 32;          // k rows per staged slab; k ranges of a split are multiples of it
+// Channels per thread block: 16, or 32 when there are more than 16 (an MMA of 32 or 64 output
+// columns holds the tensor pipe as long as one of 16 or 32); n rows per thread block that go with it
+// (tensor memory holds four row groups of 128 pairs at 16 channels, two at 32).
+inline int gt_ot_for(int o) { return o > 16 ? 32 : 16; }
+int gt_rg_for(int ot);                                 // row groups of 128 pairs per thread block
+inline int gt_tn_for(int ot) { return 4 * gt_rg_for(ot); }
+int gt_blocks_per_sm(int ot);
+constexpr int GT_NORM_SQRT = 3;
+struct GradTensorParams {
+    int M, N, O, K, L;
+    const float* A; long long lda, a_sl;
+    const float* B; long long ldb, b_sl;
+    const float* C; long long ldc, c_sl;
+    const float* D; long long ldd, d_sl;
+    float*       E; long long e_sn, e_so, e_sl;   // destination (out, or scratch when split)
+    KmHyper p;
+    int ot;                                         // channels per thread block: 16 or 32
+    int rg;                                         // row groups per thread block
+    int tiles_m, tiles_n, o_chunks, splits;
+    int k_per_split;
+    long long split_stride;
+    int c_vec;                                      // c rows can be read 16 bytes at a time
+};
+int grad_tensor_launch(const GradTensorParams& p, int norm_kind, cudaStream_t st);
+// Reads back and clears the wait-ran-out flag of the tensor-core gradient kernel; the device
+// must already be synchronised.  0 / 1, or -1 on error.
+int grad_tensor_take_wait_flag();
+
 inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

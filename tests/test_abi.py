@@ -224,6 +224,16 @@ def test_grad_rejects_bad_arguments():
     g.lda = 8
     g.split_k = 4       # asks for a split without providing scratch: rejected before any launch
     assert lib.kermac_b200_cdist_grad_scratch_bytes(ctypes.byref(g)) == 4 * 8 * 8 * 2 * 4
+    g.split_k = 0
+    g.contraction = 3   # not a KM_CONTRACT_*
+    assert lib.kermac_b200_cdist_grad(ctypes.byref(g), None) == -4
+    # the tensor-core form plans its k split for its own tiles (32 x 16 pairs, one block per SM):
+    # 2 x 1 tiles of a 64 x 16 output and 4096 k leave room for a split, whichever kernel runs
+    g.contraction, g.m, g.n, g.k = 2, 64, 16, 4096
+    g.lda = g.ldd = g.out_stride_n = 64
+    g.ldb = g.ldc = 4096
+    g.out_stride_o = 64 * 16
+    assert lib.kermac_b200_cdist_grad_scratch_bytes(ctypes.byref(g)) % (64 * 16 * 2 * 4) == 0
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

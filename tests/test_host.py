@@ -215,6 +215,12 @@ def test_cdist_grad_marshalling_and_norm_selection(recorder, monkeypatch):
     pt = torch.tensor([1.5, 2.5])
     kermac.cdist_grad(a, b, c, d, p=pt)
     assert recorder[-1][1].norm_type == _native.NORM_P and recorder[-1][1].p.ptr == pt.data_ptr()
+    # where the products with c run: KM_CONTRACT_AUTO / _FP32 / _TENSOR
+    assert recorder[-1][1].contraction == 0
+    kermac.cdist_grad(a, b, c, d, p=1.0, contraction="fp32")
+    assert recorder[-1][1].contraction == 1
+    kermac.cdist_grad(a, b, c, d, p=1.0, contraction="tensor")
+    assert recorder[-1][1].contraction == 2
     # a 3-D out with a batch of one is read as unbatched
     a1, b1, c1, d1 = _grad_inputs()
     out3 = torch.zeros(3, 5, 6)
@@ -234,6 +240,8 @@ def test_cdist_grad_validation_errors(recorder):
         kermac.cdist_grad(a, b, c, d, out=torch.zeros(3, 5, 7))
     with pytest.raises(TypeError):
         kermac.cdist_grad(a, b, c, d.double())
+    with pytest.raises(ValueError, match="contraction must be one of"):
+        kermac.cdist_grad(a, b, c, d, contraction="bf16")
     assert not recorder
 
 
