@@ -302,15 +302,19 @@ def grad(args, ctx):
     fp_out = out2.clone()
     t_tc = _timed(run(lambda: kermac.cdist_grad(ad, bd, c2, dd, out=out2, p=1.0, contraction="tensor")), few, 1, ctx.barrier) - t_flush
     mmas = (float(M) * N / 128.0) * (K / 8.0) * 2.0
-    sms = torch.cuda.get_device_properties(0).multi_processor_count
-    mma_rate = sms * (line["clocks"].get("sm_mhz") or 1965.0) * 1e6 / 45.0
+    mma_rate = _native.measure_pipe(9, 4096)[0]                    # 128 x 64 x 8, issued back to back on every SM
     line["O=32"] = {"fp32_kernel_ms": t_fp, "tensor_kernel_ms": t_tc, "ratio": t_fp / t_tc,
                     "max_abs_diff_over_max": float((out2 - fp_out).abs().max() / fp_out.abs().max()),
                     "device_error_flag": _native.device_error_flag(),
                     "roofline": {"bound": "tensor", "achieved": mmas / (t_tc * 1e-3) / 1e9, "peak": mma_rate / 1e9,
                                  "unit": "G narrow-MMA/s", "frac": mmas / (t_tc * 1e-3) / mma_rate, "traffic": None,
-                                 "note": "tcgen05.mma kind::tf32 128 x N x 8 with N <= 64: ~45 cycles each whatever N "
-                                         "(a quarter of the pipe's rate at N = 32, half at N = 64); 2 per 128 pairs x 8 k"}}
+                                 "peak_source": "measured on this device by kermac_b200_measure_pipe kind 9",
+                                 "mma_per_s_n32_n64_n128_n256": [_native.measure_pipe(8, 4096)[0], mma_rate,
+                                                                 _native.measure_pipe(10, 4096)[0],
+                                                                 _native.measure_pipe(11, 4096)[0]],
+                                 "note": "tcgen05.mma kind::tf32 128 x N x 8 with N <= 64 holds the tensor pipe ~45 cycles "
+                                         "whatever N (a quarter of the pipe's rate at N = 32, half at N = 64); 2 per 128 "
+                                         "pairs x 8 k (head and remainder of the weights)"}}
     if not args.no_ref_gpu:
         from baseline import ref_kernels
         if ref_kernels.available():

@@ -261,6 +261,10 @@ int kermac_b200_describe_variant(const KmBuildArgs* args, char* buf, int32_t buf
  *           sign flip, four packed FMAs with three different register-pair sources per (m, n) pair)
  *           -> FP32 lane-operations per second (1 + 4 per (m, n, k))
  *   kind 7: the same with the channel FMAs as scalar instructions
+ *   kind 8 .. 11: tcgen05.mma kind::tf32 of 128 rows x N columns x 8 k with the A operand in tensor
+ *           memory, N = 32, 64, 128, 256, issued back to back by one thread per SM (8 per iteration)
+ *           -> MMAs per second over all SMs (the narrow ones of the tensor-core gradient kernel hold
+ *           the pipe ~45 cycles whatever N up to 64)
  * Synchronises the device.  Returns 0 and stores the rate in *ops_per_second.
  */
 int kermac_b200_measure_pipe(int32_t kind, int32_t iterations, double* ops_per_second, double* milliseconds);

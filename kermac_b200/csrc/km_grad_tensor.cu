@@ -39,9 +39,10 @@
 // for no more than ~20 warps.  Hence the automatic choice: tensor cores from 17 channels on, where the
 // FP32 kernel needs a second pass.
 //
-// Hand-over between the warps is by mbarriers (spun on with the non-blocking test: they change hands
-// every few hundred cycles); every wait is bounded, and a wait that runs out sets a flag
-// (kermac_b200_device_error_flag) and lets the block run to its end without its results.
+// Hand-over between the warps is by mbarriers; every wait is bounded, and a wait that runs out sets a
+// flag (kermac_b200_device_error_flag) and lets the block run to its end without its results.  (Spinning
+// on the non-blocking mbarrier test instead of the suspending try_wait measured 1 % slower and tripled
+// the instructions executed.)
 #include "km_common.cuh"
 #include "km_host.h"
 #include "km_mbar.cuh"
@@ -91,7 +92,6 @@ __device__ int g_grad_tensor_wait_expired = 0;
 template <int THREADS>
 __device__ __forceinline__ void generators_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory"); }
 
-#define GT_WAIT mbar_spin_bounded
 
 // 16 weights of one (n, m) row: k = 0..15 of arow (a transposed) and brow, split into hi / lo.
 template <int NORM, bool TAIL>
@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
         };
         auto drain = [&](int c) {
             const int set = c & 1;
-            if (!expired && !GT_WAIT(dfull(set), (c >> 1) & 1)) expired = true;
+            if (!expired && !mbar_wait_bounded(dfull(set), (c >> 1) & 1)) expired = true;
             __syncwarp();
             tc::fence_after_sync();
 #pragma unroll
@@ -311,7 +311,7 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
                 }
                 // the MMAs that read this buffer NB steps ago must be done before it is overwritten
                 {
-                    if (t >= NB && !expired && !GT_WAIT(aempty(t % NB), (t / NB - 1) & 1)) expired = true;
+                    if (t >= NB && !expired && !mbar_wait_bounded(aempty(t % NB), (t / NB - 1) & 1)) expired = true;
                     __syncwarp();
                    
                 }
@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
             for (int s = 0; s < nslabs; ++s) {
                 const int slot           = s % GT_C_SLOTS;
                 const uint32_t slot_addr = c_addr + slot * S::C_BYTES;
-                { if (!expired && !GT_WAIT(cfull(slot), (s / GT_C_SLOTS) & 1)) expired = true; }
+                { if (!expired && !mbar_wait_bounded(cfull(slot), (s / GT_C_SLOTS) & 1)) expired = true; }
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     const int t     = 2 * s + hf;
@@ -354,7 +354,7 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
                     const uint32_t d0  = tmem + is * RG_PER * S::RG_COLS + S::D_OFF + set * S::D_COLS;
                     const uint32_t a0  = tmem + is * RG_PER * S::RG_COLS + (t % NB) * GT_A_COLS;
                     {
-                        if (!expired && !GT_WAIT(afull(is, t % NB), (t / NB) & 1)) expired = true;
+                        if (!expired && !mbar_wait_bounded(afull(is, t % NB), (t / NB) & 1)) expired = true;
                         tc::fence_after_sync();
                        
                     }
@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
             float nx[CHUNKS][4];
             if (s + 1 < nslabs) load_c(s + 1, nx);
             // the MMAs that read this slot four slabs ago must be done
-            if (s >= GT_C_SLOTS && !expired && !GT_WAIT(cfree(slot), ((s / GT_C_SLOTS) - 1) & 1)) expired = true;
+            if (s >= GT_C_SLOTS && !expired && !mbar_wait_bounded(cfree(slot), ((s / GT_C_SLOTS) - 1) & 1)) expired = true;
             __syncwarp();
             unsigned char* dst = c_tiles + slot * S::C_BYTES;
 #pragma unroll

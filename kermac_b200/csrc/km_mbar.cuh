@@ -49,26 +49,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, int parity, int 
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
-// The same wait as a spin on the non-blocking test: a thread suspended in try_wait can take
-// microseconds to resume after the phase completes, which a hand-over on a latency-critical path
-// (tensor-memory buffers passed between warps every few hundred cycles) cannot afford.
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, int parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-constexpr int MBAR_SPIN_TRIES = 1 << 24;
-__device__ __forceinline__ bool mbar_spin_bounded(uint32_t bar, int parity, int tries = MBAR_SPIN_TRIES) {
-    for (int i = 0; i < tries; ++i)
-        if (mbar_test_wait(bar, parity)) return true;
-    return false;
-}
 // Tiled TMA copy (no multicast) of one box of a rank-3 tensor into shared memory; the
 // mbarrier receives the byte count.  x is the innermost coordinate: x * 4 bytes must be a
 // multiple of 16.

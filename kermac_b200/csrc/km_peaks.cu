@@ -4,6 +4,8 @@
 // runs at, instead of a nominal figure.
 #include "km_build_params.cuh"
 #include "km_host.h"
+#include "km_mbar.cuh"
+#include "km_tcgen05.cuh"
 
 namespace km {
 namespace {
@@ -162,6 +164,42 @@ __global__ void __launch_bounds__(256, 2) grad_step_kernel(float* sink, int step
 
 typedef void (*PipeFn)(float*, int, float);
 
+// Issue rate of the narrow MMAs of the tensor-core gradient kernel: one thread per SM issues
+// tcgen05.mma kind::tf32, 128 rows x N columns x 8 k, A operand from tensor memory, B from shared
+// memory, all into one accumulator (the pipe does not wait on a dependent accumulate).  Operand values
+// are whatever the memories hold; only the time matters.  The wait for the last MMA is bounded.
+template <int N>
+__global__ void __launch_bounds__(128) mma_rate_kernel(float* sink, int steps, float) {
+    __shared__ __align__(1024) unsigned char b_tile[256 * 128];
+    __shared__ __align__(8) unsigned long long s_bar;
+    __shared__ uint32_t s_tmem;
+    for (int i = threadIdx.x; i < 256 * 128 / 4; i += blockDim.x) reinterpret_cast<float*>(b_tile)[i] = 0.0f;
+    const uint32_t bar = smem_u32(&s_bar);
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (threadIdx.x < 32) tc::tmem_alloc(smem_u32(&s_tmem), 512);
+    tc::fence_smem_to_async();
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem = s_tmem;
+    if (threadIdx.x == 0) {
+        constexpr uint32_t idesc = tc::instr_desc_tf32(128, N);
+        const uint64_t db        = tc::smem_desc_k_major_sw128(smem_u32(b_tile));
+        for (int it = 0; it < steps; ++it) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) tc::mma_tf32_a_tmem(tmem + 256, tmem + j * 8, db, idesc, true);
+        }
+        tc::commit(bar);
+        if (!mbar_wait_bounded(bar, 0)) sink[1] = 1.0f;
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x < 32) tc::tmem_dealloc(tmem, 512);
+}
+
 }  // namespace
 }  // namespace km
 
@@ -169,21 +207,24 @@ extern "C" int kermac_b200_measure_pipe(int32_t kind, int32_t iterations, double
                                         double* milliseconds) {
     using namespace km;
     if (!ops_per_second) return fail(KM_ERR_NULL_POINTER, "ops_per_second is NULL");
-    if (kind < 0 || kind > 7) return fail(KM_ERR_BAD_ENUM, "kind %d is not a pipe benchmark", kind);
+    if (kind < 0 || kind > 11) return fail(KM_ERR_BAD_ENUM, "kind %d is not a pipe benchmark", kind);
     if (iterations < 1 || iterations > (1 << 24)) return fail(KM_ERR_BAD_SHAPE, "iterations out of range");
     if (int rc = require_sm100()) return rc;
-    PipeFn fns[8] = {pipe_kernel<0>, pipe_kernel<1>, pipe_kernel<2>, pipe_kernel<3>,
-                     inner_loop_kernel<IN_DIFF_SQUARE>, inner_loop_kernel<IN_DIFF_ABS>,
-                     grad_step_kernel<true>, grad_step_kernel<false>};
+    PipeFn fns[12] = {pipe_kernel<0>, pipe_kernel<1>, pipe_kernel<2>, pipe_kernel<3>,
+                      inner_loop_kernel<IN_DIFF_SQUARE>, inner_loop_kernel<IN_DIFF_ABS>,
+                      grad_step_kernel<true>, grad_step_kernel<false>,
+                      mma_rate_kernel<32>, mma_rate_kernel<64>, mma_rate_kernel<128>, mma_rate_kernel<256>};
     float* sink   = nullptr;
     if (int rc = cuda_status(cudaMalloc(&sink, 256), "cudaMalloc")) return rc;
-    const int blocks = sm_count() * (kind >= 4 ? 2 : 8);
+    const bool mma   = kind >= 8;
+    const int blocks = sm_count() * (mma ? 1 : (kind >= 4 ? 2 : 8));
+    const int threads = mma ? 128 : PEAK_THREADS;
     cudaEvent_t e0, e1;
     cudaEventCreate(&e0);
     cudaEventCreate(&e1);
-    fns[kind]<<<blocks, PEAK_THREADS>>>(sink, iterations / 8 + 1, 1.5f);   // warm-up
+    fns[kind]<<<blocks, threads>>>(sink, iterations / 8 + 1, 1.5f);   // warm-up
     cudaEventRecord(e0);
-    fns[kind]<<<blocks, PEAK_THREADS>>>(sink, iterations, 1.5f);
+    fns[kind]<<<blocks, threads>>>(sink, iterations, 1.5f);
     cudaEventRecord(e1);
     int rc = cuda_status(cudaEventSynchronize(e1), "pipe benchmark");
     float ms = 0.0f;
@@ -199,6 +240,8 @@ extern "C" int kermac_b200_measure_pipe(int32_t kind, int32_t iterations, double
     if (kind >= 4) total = 2.0 * 64.0 * (BUILD_CPA_BK - 4) * (double)iterations * (double)blocks * PEAK_THREADS;
     // gradient-step kinds: 4 steps per iteration, 16 (m, n) pairs per thread and step, 1 + 4 lane-ops each
     if (kind >= 6) total = 4.0 * 16.0 * 5.0 * (double)iterations * (double)blocks * PEAK_THREADS;
+    // MMA kinds: 8 MMAs per iteration and SM
+    if (mma) total = 8.0 * (double)iterations * (double)blocks;
     *ops_per_second       = total / (ms * 1e-3);
     if (milliseconds) *milliseconds = ms;
     return 0;
