@@ -30,7 +30,7 @@
 // and two accumulator sets (2 x 2 OT columns); the block takes all 512 columns of its SM and runs
 // alone there: OT = 16 with 4 row groups (16 n), OT = 32 with 2 (8 n).
 //
-// What bounds it (B200, K = 30000, M = 4096, N = 256, p = 1: 22.9 ms at 16 channels, 28.9 ms at 32,
+// What bounds it (B200, K = 30000, M = 4096, N = 256, p = 1: 22.6 ms at 16 channels, 28.6 ms at 32,
 // against 20.4 / 40.4 ms of the FP32 kernel): a tcgen05.mma kind::tf32 of 128 rows x 8 k holds the
 // tensor pipe for max(45, N / 2) cycles whatever its width N, so the narrow MMAs of this product run
 // the pipe at a quarter (N = 32) or half (N = 64) of its rate: 9.5 ms of MMAs per pass alone.  The
