@@ -151,7 +151,7 @@ int64_t kermac_b200_build_tile_count(const KmBuildArgs* args);
  * thread blocks (see kermac_b200_cdist_grad_scratch_bytes).
  * `contraction` (KM_CONTRACT_*, defined below with kermac_b200_kernel_matvec) selects where the
  * products with c run: KM_CONTRACT_FP32 as packed FP32 FMAs; KM_CONTRACT_TENSOR on the tcgen05
- * tensor cores, up to 32 channels at a time, as three tf32 products per term (weights and
+ * tensor cores, up to 64 channels at a time, as three tf32 products per term (weights and
  * coefficients split into a tf32 head and an fp32 remainder, accumulation chains of 128 k added up
  * in fp32: fp32-level accuracy, not the FP32 kernel's bits); KM_CONTRACT_AUTO takes the tensor
  * cores from 17 channels and 256 k on.  The weights a * g(d - b) are computed in FP32 either way.  A bounded

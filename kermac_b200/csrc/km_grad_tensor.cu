@@ -25,17 +25,19 @@
 //
 // Work decomposition: a thread block owns 32 (m) x 4 RG (n) pairs = RG row groups of 128 pairs and
 // up to OT channels.  4 RG warps generate weights (4 per row group, one per quarter of the tensor-memory
-// lanes), two warps issue the MMAs (half of the row groups each), one warp splits and parks the
+// lanes), two warps issue the MMAs (half of the row groups each), one or two warps split and park the
 // coefficients.  Per row group tensor memory holds two A buffers of 16 k (hi and lo: 2 x 32 columns)
-// and two accumulator sets (2 x 2 OT columns); the block takes all 512 columns of its SM and runs
-// alone there: OT = 16 with 4 row groups (16 n), OT = 32 with 2 (8 n).
+// and the accumulators (2 OT columns per set); the block allocates all 512 columns of its SM and runs
+// alone there: OT = 16 with 4 row groups (16 n) and OT = 32 with 2 (8 n), two accumulator sets each;
+// OT = 64 with 2 row groups and one accumulator set (the next chain's MMAs wait until the generating
+// warps have read the finished one).
 //
-// What bounds it (B200, K = 30000, M = 4096, N = 256, p = 1: 22.6 ms at 16 channels, 28.6 ms at 32,
-// against 20.4 / 40.4 ms of the FP32 kernel): a tcgen05.mma kind::tf32 of 128 rows x 8 k holds the
-// tensor pipe for max(45, N / 2) cycles whatever its width N, so the narrow MMAs of this product run
-// the pipe at a quarter (N = 32) or half (N = 64) of its rate: 9.5 ms of MMAs per pass alone.  The
-// weight generation (11 ms alone), the tensor-memory stores (+5 to 8 ms) and the MMAs (+4 to 7 ms)
-// overlap only in part: tensor memory has room for two A buffers per row group, and the registers
+// What bounds it (B200, K = 30000, M = 4096, N = 256, p = 1: 22.4 ms at 16 channels, 28.0 at 32, 36.7
+// at 64, against 20.4 / 40.4 / 80.7 ms of the FP32 kernel): a tcgen05.mma kind::tf32 of 128 rows x 8 k
+// holds the tensor pipe for max(45, N / 2) cycles whatever its width N, so the narrow MMAs of this product
+// run the pipe at a quarter (N = 32) or half (N = 64) of its rate: 9.5 ms of MMAs per pass alone.  At 16
+// channels the weight generation (11 ms alone), the tensor-memory stores (+5 to 8 ms) and the MMAs (+4 to
+// 7 ms) overlap only in part: tensor memory has room for two A buffers per row group, and the registers
 // for no more than ~20 warps.  Hence the automatic choice: tensor cores from 17 channels on, where the
 // FP32 kernel needs a second pass.
 //
@@ -67,16 +69,23 @@ struct GtShape {
     static constexpr int GEN_WARPS    = 4 * RG;
     static constexpr int GEN_THREADS  = 32 * GEN_WARPS;
     static constexpr int ISSUERS      = RG >= 2 ? 2 : 1;           // warps that issue MMAs, RG / ISSUERS row groups each
-    static constexpr int THREADS      = GEN_THREADS + 32 * (ISSUERS + 1);   // + the MMA warps and the coefficient warp
+    // warps that park the coefficients: one was the slowest warp of the block from 32 channels on (64 channels:
+    // 48.3 ms with one, 36.7 with two; four cost registers the generating warps need: 40.6)
+    static constexpr int C_WARPS      = OT >= 32 ? 2 : 1;
+    static constexpr int THREADS      = GEN_THREADS + 32 * (ISSUERS + C_WARPS);   // + the MMA warps and the coefficient warps
     static constexpr int TN           = 4 * RG;                    // n rows of the tile
     static constexpr int STAGE_FLOATS = GT_TM * GT_PA + TN * GT_PB;
     static constexpr int C_BYTES      = 2 * OT * 128;              // 2 OT rows (c_hi, c_lo) of 32 k
     static constexpr int D_COLS       = 2 * OT;                    // one accumulator set: main, correction
+    // Accumulator sets per row group.  Two alternate, so that a finished chain is added up while the next one
+    // runs; at 64 channels tensor memory has room for one, and the MMAs of the next chain wait for the
+    // generating warps to have read the finished one.
+    static constexpr int SETS         = OT >= 64 ? 1 : 2;
     // A buffers of 16 k per row group.  Four of them (at two row groups) measured slower than two:
     // 33.8 against 28.9 ms at 32 channels.
     static constexpr int A_BUFS       = 2;
     static constexpr int D_OFF        = A_BUFS * GT_A_COLS;        // accumulator sets start after the A buffers
-    static constexpr int RG_COLS      = D_OFF + 2 * D_COLS;        // tensor-memory columns per row group
+    static constexpr int RG_COLS      = D_OFF + SETS * D_COLS;     // tensor-memory columns per row group
     static constexpr int TMEM_COLS    = gt_pow2_cols(RG * RG_COLS);  // allocated (a power of two)
     static constexpr int BLOCKS_PER_SM = 512 / TMEM_COLS;          // as many blocks as tensor memory holds
     // Shared memory asked for: more than 1 / (BLOCKS_PER_SM + 1) of an SM's, so that no more blocks become
@@ -142,7 +151,7 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
     extern __shared__ unsigned char smem_raw[];
     // afull[rg][buf] (one arrival per generating warp of the row group), aempty[buf], dfull[set], cfree[slot]
     // (tcgen05.commit), cfull[slot] (the coefficient warp)
-    __shared__ __align__(8) unsigned long long s_bars[S::ISSUERS * S::A_BUFS + S::A_BUFS + 2 + 2 * GT_C_SLOTS];
+    __shared__ __align__(8) unsigned long long s_bars[S::ISSUERS * S::A_BUFS + S::A_BUFS + 2 + 2 * GT_C_SLOTS + S::ISSUERS];
     __shared__ uint32_t s_tmem;
 
     const uint32_t raw_addr = smem_u32(smem_raw);
@@ -178,14 +187,17 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
     auto dfull  = [&](int set) { return bars + 8u * (NI * NB + NB + set); };
     auto cfull  = [&](int slot) { return bars + 8u * (NI * NB + NB + 2 + slot); };
     auto cfree  = [&](int slot) { return bars + 8u * (NI * NB + NB + 2 + GT_C_SLOTS + slot); };
+    auto dfree  = [&](int is) { return bars + 8u * (NI * NB + NB + 2 + 2 * GT_C_SLOTS + is); };   // single accumulator set only
+    constexpr int SETS = S::SETS;
 
     if (tid == 0) {
         for (int is = 0; is < NI; ++is)
             for (int b = 0; b < NB; ++b) mbar_init(afull(is, b), 4 * RG_PER);  // the generating warps of its row groups
         for (int b = 0; b < NB; ++b) mbar_init(aempty(b), NI);                  // one tcgen05.commit per issuer
         for (int b = 0; b < 2; ++b) mbar_init(dfull(b), NI);
+        for (int is = 0; is < NI; ++is) mbar_init(dfree(is), 4 * RG_PER);
         for (int sl = 0; sl < GT_C_SLOTS; ++sl) {
-            mbar_init(cfull(sl), 1);
+            mbar_init(cfull(sl), S::C_WARPS);
             mbar_init(cfree(sl), NI);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -256,8 +268,8 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
             cp_async_4(base + b_dst, ok ? b_src + ks : p.B, ok ? 4 : 0);
         };
         auto drain = [&](int c) {
-            const int set = c & 1;
-            if (!expired && !mbar_wait_bounded(dfull(set), (c >> 1) & 1)) expired = true;
+            const int set = SETS == 2 ? (c & 1) : 0;
+            if (!expired && !mbar_wait_bounded(dfull(set), (SETS == 2 ? (c >> 1) : c) & 1)) expired = true;
             __syncwarp();
             tc::fence_after_sync();
 #pragma unroll
@@ -269,6 +281,11 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
                 for (int i = 0; i < 16; ++i) run[part * 16 + i] += __uint_as_float(r0[i]) + __uint_as_float(r1[i]);
             }
             tc::fence_before_sync();
+            if constexpr (SETS == 1) {
+                // the one accumulator set may be started over
+                __syncwarp();
+                if (lane == 0) mbar_arrive(dfree(rg / RG_PER));
+            }
         };
         // hands the A buffer of step t to the MMA warp, once its tensor-memory stores have landed
         auto publish = [&](int t) {
@@ -304,7 +321,8 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
                 else                 weights16<NORM, true>(hi, lo, sa + hf * GT_KA, sb + hf * GT_KA, dd, pm1, kvalid - hf * GT_KA);
                 { if (t > 0) publish(t - 1); }
                 // the chain before the running one finished a buffer ago: add it to the running sums
-                if (t == GT_CHAIN * next_drain + GT_CHAIN + 1) {
+                // (with a single accumulator set: at the first step of the next chain, which cannot start before)
+                if (t == GT_CHAIN * next_drain + GT_CHAIN + (SETS == 2 ? 1 : 0)) {
                     drain(next_drain);
                     ++next_drain;
                    
@@ -346,7 +364,7 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     const int t     = 2 * s + hf;
-                    const int set   = (t / GT_CHAIN) & 1;
+                    const int set   = SETS == 2 ? (t / GT_CHAIN) & 1 : 0;
                     const bool head = (t % GT_CHAIN) == 0;
                     const bool tail = (t % GT_CHAIN) == GT_CHAIN - 1 || t == T - 1;
                     const uint64_t db0 = tc::smem_desc_k_major_sw128(slot_addr + (hf * 2) * 32);
@@ -355,6 +373,7 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
                     const uint32_t a0  = tmem + is * RG_PER * S::RG_COLS + (t % NB) * GT_A_COLS;
                     {
                         if (!expired && !mbar_wait_bounded(afull(is, t % NB), (t / NB) & 1)) expired = true;
+                        if (SETS == 1 && head && t > 0 && !expired && !mbar_wait_bounded(dfree(is), (t / GT_CHAIN - 1) & 1)) expired = true;
                         tc::fence_after_sync();
                        
                     }
@@ -388,7 +407,9 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
         // ------------------------------------------------------------------ coefficient warp
         // A slab's OT x 32 coefficients, split into hi / lo and parked as the MMA's B operand: K-major rows
         // of 128 bytes with the 128-byte swizzle, rows 0..OT-1 c_hi, rows OT..2 OT-1 c_lo.
-        constexpr int CHUNKS = OT / 4;                 // 16-byte chunks per lane and slab
+        constexpr int CPW    = OT / S::C_WARPS;        // channels this warp parks
+        constexpr int CHUNKS = CPW / 4;                // 16-byte chunks per lane and slab
+        const int cw0        = (warp - S::GEN_WARPS - NI) * CPW;
         const float* C = p.C + (long long)l * p.c_sl;
         float cv[CHUNKS][4];
         auto load_c = [&](int s, float (&v)[CHUNKS][4]) {
@@ -396,7 +417,7 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
 #pragma unroll
             for (int i = 0; i < CHUNKS; ++i) {
                 const int id = lane + 32 * i;
-                const int o = id >> 3, ck = id & 7;
+                const int o = cw0 + (id >> 3), ck = id & 7;
                 const int gk = k0 + 4 * ck;
                 const bool o_ok = (o0 + o) < p.O;
                 const float* src = C + (long long)(o0 + o) * p.ldc + gk;
@@ -421,7 +442,7 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
 #pragma unroll
             for (int i = 0; i < CHUNKS; ++i) {
                 const int id = lane + 32 * i;
-                const int o = id >> 3, ck = id & 7;
+                const int o = cw0 + (id >> 3), ck = id & 7;
                 float hi[4], lo[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -482,13 +503,14 @@ int grad_tensor_launch_shape(const GradTensorParams& p, int norm_kind, cudaStrea
 int grad_tensor_launch(const GradTensorParams& p, int norm_kind, cudaStream_t st) {
     if (p.ot == 16 && p.rg == 4) return grad_tensor_launch_shape<16, 4>(p, norm_kind, st);
     if (p.ot == 32 && p.rg == 2) return grad_tensor_launch_shape<32, 2>(p, norm_kind, st);
+    if (p.ot == 64 && p.rg == 2) return grad_tensor_launch_shape<64, 2>(p, norm_kind, st);
     return fail(KM_ERR_INTERNAL, "no tensor-core gradient kernel for %d channels x %d row groups per block", p.ot, p.rg);
 }
 
 // Row groups per block: as many as tensor memory holds (two A buffers of 32 columns and two accumulator
 // sets of 2 OT columns per row group).
-int gt_rg_for(int ot) { return ot == 32 ? 2 : 4; }
-int gt_blocks_per_sm(int ot) { return ot == 32 ? GtShape<32, 2>::BLOCKS_PER_SM : GtShape<16, 4>::BLOCKS_PER_SM; }
+int gt_rg_for(int ot) { return ot >= 32 ? 2 : 4; }
+int gt_blocks_per_sm(int ot) { return ot == 64 ? GtShape<64, 2>::BLOCKS_PER_SM : ot == 32 ? GtShape<32, 2>::BLOCKS_PER_SM : GtShape<16, 4>::BLOCKS_PER_SM; }
 
 int grad_tensor_take_wait_flag() {
     int v = 0, zero = 0;

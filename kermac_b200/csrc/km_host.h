@@ -32,10 +32,10 @@ int matvec_take_wait_flag();
 // GT_NORM_SQRT (|x|^(1/2), chosen by the caller for a host scalar p = 1.5).
 constexpr int GT_TM = 32;          // m per thread block
 constexpr int GT_BK = 32;          // k rows per staged slab; k ranges of a split are multiples of it
-// Channels per thread block: 16, or 32 when there are more than 16 (an MMA of 32 or 64 output
-// columns holds the tensor pipe as long as one of 16 or 32); n rows per thread block that go with it
-// (tensor memory holds four row groups of 128 pairs at 16 channels, two at 32).
-inline int gt_ot_for(int o) { return o > 16 ? 32 : 16; }
+// Channels per thread block: 16, 32 or 64, the smallest that holds them all (an MMA of up to 64 output
+// columns holds the tensor pipe as long as one of 16, one of 128 only 1.4 times as long); n rows per thread
+// block that go with it (tensor memory holds four row groups of 128 pairs at 16 channels, two at 32 and 64).
+inline int gt_ot_for(int o) { return o > 32 ? 64 : (o > 16 ? 32 : 16); }
 int gt_rg_for(int ot);                                 // row groups of 128 pairs per thread block
 inline int gt_tn_for(int ot) { return 4 * gt_rg_for(ot); }
 int gt_blocks_per_sm(int ot);
@@ -48,7 +48,7 @@ struct GradTensorParams {
     const float* D; long long ldd, d_sl;
     float*       E; long long e_sn, e_so, e_sl;   // destination (out, or scratch when split)
     KmHyper p;
-    int ot;                                         // channels per thread block: 16 or 32
+    int ot;                                         // channels per thread block: 16, 32 or 64
     int rg;                                         // row groups per thread block
     int tiles_m, tiles_n, o_chunks, splits;
     int k_per_split;

@@ -25,9 +25,10 @@ def clean_flag():
 
 
 @pytest.mark.parametrize("p", [1.0, 1.5, 2.0, 3.0, 0.5])
-@pytest.mark.parametrize("O", [1, 7, 16, 17, 32, 33, 70])
+@pytest.mark.parametrize("O", [1, 7, 16, 17, 32, 33, 64, 70])
 def test_every_channel_tile_and_norm(p, O):
-    # K = 37: one full slab and a ragged one; M, N not multiples of the 32 x 16 / 32 x 8 tiles
+    # K = 37: one full slab and a ragged one; M, N not multiples of the 32 x 16 / 32 x 8 tiles; channel counts on
+    # both sides of the 16-, 32- and 64-channel shapes
     K, M, N = 37, 70, 45
     a, b, c, d = gen((K, M), 5, "rand"), gen((N, K), 6), gen((O, K), 7), gen((N, M), 8)
     got = kermac.cdist_grad(a.cuda(), b.cuda(), c.cuda(), d.cuda(), p=p, contraction="tensor")
@@ -36,10 +37,12 @@ def test_every_channel_tile_and_norm(p, O):
     clean_flag()
 
 
+@pytest.mark.parametrize("O", [16, 40])
 @pytest.mark.parametrize("K", [1, 15, 16, 17, 31, 32, 33, 127, 128, 129, 255, 257, 1000])
-def test_k_extents_around_buffers_slabs_and_chains(K):
-    # 16 k per tensor-memory buffer, 32 per slab, 128 per accumulator chain
-    M, N, O = 40, 20, 16
+def test_k_extents_around_buffers_slabs_and_chains(K, O):
+    # 16 k per tensor-memory buffer, 32 per slab, 128 per accumulator chain; 40 channels take the shape with one
+    # accumulator set, whose chains hand over differently
+    M, N = 40, 20
     a, b, c, d = gen((K, M), 9, "rand"), gen((N, K), 10), gen((O, K), 11), gen((N, M), 12)
     for p in (1.0, 2.0):
         got = kermac.cdist_grad(a.cuda(), b.cuda(), c.cuda(), d.cuda(), p=p, contraction="tensor")
@@ -86,7 +89,7 @@ def test_batching_broadcast_and_per_batch_p():
     clean_flag()
 
 
-@pytest.mark.parametrize("O", [16, 40])
+@pytest.mark.parametrize("O", [16, 24, 40])
 def test_same_sign_sums_stay_at_fp32_accuracy(O):
     # Every term positive, 20000 of them: a chain of truncating tensor-core additions that long would
     # drift by ~1e-4; cut every 128 k and added up in FP32 the result stays within 3e-6 of the oracle.
@@ -99,7 +102,7 @@ def test_same_sign_sums_stay_at_fp32_accuracy(O):
     clean_flag()
 
 
-@pytest.mark.parametrize("O", [16, 32])
+@pytest.mark.parametrize("O", [16, 32, 48])
 def test_split_k_through_the_c_abi(O):
     K, M, N = 3000, 96, 40
     a, b, c, d = gen((K, M), 28, "rand"), gen((N, K), 29), gen((O, K), 30), gen((N, M), 31)
