@@ -291,30 +291,35 @@ def grad(args, ctx):
     line["roofline"]["inner_step_ceiling_lane_ops"] = step_packed
     line["roofline"]["frac_of_inner_step_ceiling"] = (1.0 + O) * triples / (ms1 * 1e-3) / step_packed
     line["roofline"]["inner_step_ceiling_scalar_fma_lane_ops"] = step_scalar
-    # 32 channels: the tensor-core kernel (the automatic choice from 17 channels on) next to the FP32 kernel.
+    # 32 and 64 channels: the tensor-core kernel (the automatic choice from 17 channels on) next to the FP32 kernel.
     # Its bound is the tensor pipe at the rate narrow MMAs get: a 128 x 8 tf32 MMA of up to 64 output
     # columns holds the pipe ~45 cycles; two of them (head and remainder of the weights) per 128 pairs x 8 k.
-    O2 = 32
-    c2 = torch.randn(O2, K, generator=g).cuda()
-    out2 = torch.empty(1, O2, N, M, device="cuda")
     few = max(2, args.steps // 3)
-    t_fp = _timed(run(lambda: kermac.cdist_grad(ad, bd, c2, dd, out=out2, p=1.0, contraction="fp32")), few, 1, ctx.barrier) - t_flush
-    fp_out = out2.clone()
-    t_tc = _timed(run(lambda: kermac.cdist_grad(ad, bd, c2, dd, out=out2, p=1.0, contraction="tensor")), few, 1, ctx.barrier) - t_flush
-    mmas = (float(M) * N / 128.0) * (K / 8.0) * 2.0
-    mma_rate = _native.measure_pipe(9, 4096)[0]                    # 128 x 64 x 8, issued back to back on every SM
-    line["O=32"] = {"fp32_kernel_ms": t_fp, "tensor_kernel_ms": t_tc, "ratio": t_fp / t_tc,
-                    "max_abs_diff_over_max": float((out2 - fp_out).abs().max() / fp_out.abs().max()),
-                    "device_error_flag": _native.device_error_flag(),
-                    "roofline": {"bound": "tensor", "achieved": mmas / (t_tc * 1e-3) / 1e9, "peak": mma_rate / 1e9,
-                                 "unit": "G narrow-MMA/s", "frac": mmas / (t_tc * 1e-3) / mma_rate, "traffic": None,
-                                 "peak_source": "measured on this device by kermac_b200_measure_pipe kind 9",
-                                 "mma_per_s_n32_n64_n128_n256": [_native.measure_pipe(8, 4096)[0], mma_rate,
-                                                                 _native.measure_pipe(10, 4096)[0],
-                                                                 _native.measure_pipe(11, 4096)[0]],
-                                 "note": "tcgen05.mma kind::tf32 128 x N x 8 with N <= 64 holds the tensor pipe ~45 cycles "
-                                         "whatever N (a quarter of the pipe's rate at N = 32, half at N = 64); 2 per 128 "
-                                         "pairs x 8 k (head and remainder of the weights)"}}
+    mma_rates = [_native.measure_pipe(kind, 4096)[0] for kind in (8, 9, 10, 11)]   # 128 x {32, 64, 128, 256} x 8
+    for O2 in (32, 64):
+        c2 = torch.randn(O2, K, generator=g).cuda()
+        out2 = torch.empty(1, O2, N, M, device="cuda")
+        t_fp = _timed(run(lambda: kermac.cdist_grad(ad, bd, c2, dd, out=out2, p=1.0, contraction="fp32")), few, 1,
+                      ctx.barrier) - t_flush
+        fp_out = out2.clone()
+        t_tc = _timed(run(lambda: kermac.cdist_grad(ad, bd, c2, dd, out=out2, p=1.0, contraction="tensor")), few, 1,
+                      ctx.barrier) - t_flush
+        # per 128 pairs x 8 k: one MMA of 2 O2 columns (heads) and one of O2 columns (remainders)
+        per_step = float(M) * N / 128.0 * (K / 8.0)
+        wide, narrow = (mma_rates[1], mma_rates[0]) if O2 == 32 else (mma_rates[2], mma_rates[1])
+        t_bound = per_step / wide + per_step / narrow
+        line[f"O={O2}"] = {"fp32_kernel_ms": t_fp, "tensor_kernel_ms": t_tc, "ratio": t_fp / t_tc,
+                           "max_abs_diff_over_max": float((out2 - fp_out).abs().max() / fp_out.abs().max()),
+                           "device_error_flag": _native.device_error_flag(),
+                           "roofline": {"bound": "tensor", "achieved": 2.0 * per_step / (t_tc * 1e-3) / 1e9,
+                                        "peak": 2.0 * per_step / t_bound / 1e9, "unit": "G narrow-MMA/s",
+                                        "frac": t_bound / (t_tc * 1e-3), "traffic": None,
+                                        "peak_source": "measured on this device by kermac_b200_measure_pipe kinds 8-11",
+                                        "mma_per_s_n32_n64_n128_n256": mma_rates,
+                                        "note": "tcgen05.mma kind::tf32 128 x N x 8 holds the tensor pipe ~45 cycles up to "
+                                                "N = 64 and N / 2 cycles from 128 on; per 128 pairs x 8 k one of 2 O columns "
+                                                "(heads of the weights) and one of O columns (remainders)"}}
+        del c2, out2, fp_out
     if not args.no_ref_gpu:
         from baseline import ref_kernels
         if ref_kernels.available():
