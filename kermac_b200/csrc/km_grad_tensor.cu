@@ -57,7 +57,6 @@ constexpr int GT_STAGES  = 3;               // staged slabs of GT_BK k rows
 constexpr int GT_PA      = GT_BK + 4;       // floats per staged row of a (transposed: [m][k])
 constexpr int GT_PB      = GT_BK + 8;       // floats per staged row of b ([n][k])
 constexpr int GT_KA      = 16;              // k per tensor-memory A buffer
-constexpr int GT_CHAIN   = 8;               // A buffers per accumulator chain (128 k)
 constexpr int GT_C_SLOTS = 4;               // ring of coefficient tiles, one per slab
 constexpr int GT_A_COLS  = 2 * GT_KA;       // one A buffer: hi, lo
 constexpr int gt_pow2_cols(int cols) { return cols <= 32 ? 32 : cols <= 64 ? 64 : cols <= 128 ? 128 : cols <= 256 ? 256 : 512; }
@@ -81,6 +80,9 @@ struct GtShape {
     // runs; at 64 channels tensor memory has room for one, and the MMAs of the next chain wait for the
     // generating warps to have read the finished one.
     static constexpr int SETS         = OT >= 64 ? 1 : 2;
+    // A buffers per accumulator chain (128 k).  Twice as long saves 5 % at 64 channels (34.6 against 36.5 ms) and
+    // doubles the drift of same-sign sums (2.0e-6 against 1.1e-6 of the result over 20000 terms).
+    static constexpr int CHAIN        = 8;
     // A buffers of 16 k per row group.  Four of them (at two row groups) measured slower than two:
     // 33.8 against 28.9 ms at 32 channels.
     static constexpr int A_BUFS       = 2;
@@ -176,7 +178,7 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
     const int k_end   = min(p.K, k_begin + p.k_per_split);
     const int nslabs  = (k_end > k_begin) ? (k_end - k_begin + GT_BK - 1) / GT_BK : 0;
     const int T       = 2 * nslabs;                                   // A buffers in all
-    const int chains  = (T + GT_CHAIN - 1) / GT_CHAIN;
+    const int chains  = (T + S::CHAIN - 1) / S::CHAIN;
 
     const uint32_t bars = smem_u32(s_bars);
     constexpr int NI    = S::ISSUERS;
@@ -189,6 +191,7 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
     auto cfree  = [&](int slot) { return bars + 8u * (NI * NB + NB + 2 + GT_C_SLOTS + slot); };
     auto dfree  = [&](int is) { return bars + 8u * (NI * NB + NB + 2 + 2 * GT_C_SLOTS + is); };   // single accumulator set only
     constexpr int SETS = S::SETS;
+    constexpr int GT_CHAIN = S::CHAIN;
 
     if (tid == 0) {
         for (int is = 0; is < NI; ++is)
