@@ -305,13 +305,10 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
         }
         int next_drain = 0;
         for (int s = 0; s < nslabs; ++s) {
-            { cp_async_wait<GT_STAGES - 2>(); }
-            { generators_barrier<S::GEN_THREADS>(); }
-            {
-                if (s + GT_STAGES - 1 < nslabs) stage(s + GT_STAGES - 1);
-                cp_async_commit();
-               
-            }
+            cp_async_wait<GT_STAGES - 2>();
+            generators_barrier<S::GEN_THREADS>();
+            if (s + GT_STAGES - 1 < nslabs) stage(s + GT_STAGES - 1);
+            cp_async_commit();
             const float* sa  = stages + (s % GT_STAGES) * S::STAGE_FLOATS + mm * GT_PA;
             const float* sb  = stages + (s % GT_STAGES) * S::STAGE_FLOATS + GT_TM * GT_PA + nn * GT_PB;
             const int kvalid = k_end - (k_begin + s * GT_BK);
@@ -322,20 +319,16 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
                 // computed while the tensor-memory stores of the step before are still in flight
                 if (kvalid >= GT_BK) weights16<NORM, false>(hi, lo, sa + hf * GT_KA, sb + hf * GT_KA, dd, pm1, GT_KA);
                 else                 weights16<NORM, true>(hi, lo, sa + hf * GT_KA, sb + hf * GT_KA, dd, pm1, kvalid - hf * GT_KA);
-                { if (t > 0) publish(t - 1); }
+                if (t > 0) publish(t - 1);
                 // the chain before the running one finished a buffer ago: add it to the running sums
                 // (with a single accumulator set: at the first step of the next chain, which cannot start before)
                 if (t == GT_CHAIN * next_drain + GT_CHAIN + (SETS == 2 ? 1 : 0)) {
                     drain(next_drain);
                     ++next_drain;
-                   
                 }
                 // the MMAs that read this buffer NB steps ago must be done before it is overwritten
-                {
-                    if (t >= NB && !expired && !mbar_wait_bounded(aempty(t % NB), (t / NB - 1) & 1)) expired = true;
-                    __syncwarp();
-                   
-                }
+                if (t >= NB && !expired && !mbar_wait_bounded(aempty(t % NB), (t / NB - 1) & 1)) expired = true;
+                __syncwarp();
                 tc::fence_after_sync();
                 tc::st_32x32b_x16(t_row + (t % NB) * GT_A_COLS, hi);
                 tc::st_32x32b_x16(t_row + (t % NB) * GT_A_COLS + GT_KA, lo);
@@ -363,7 +356,7 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
             for (int s = 0; s < nslabs; ++s) {
                 const int slot           = s % GT_C_SLOTS;
                 const uint32_t slot_addr = c_addr + slot * S::C_BYTES;
-                { if (!expired && !mbar_wait_bounded(cfull(slot), (s / GT_C_SLOTS) & 1)) expired = true; }
+                if (!expired && !mbar_wait_bounded(cfull(slot), (s / GT_C_SLOTS) & 1)) expired = true;
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     const int t     = 2 * s + hf;
@@ -374,16 +367,13 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
                     const uint64_t db1 = tc::smem_desc_k_major_sw128(slot_addr + (hf * 2 + 1) * 32);
                     const uint32_t d0  = tmem + is * RG_PER * S::RG_COLS + S::D_OFF + set * S::D_COLS;
                     const uint32_t a0  = tmem + is * RG_PER * S::RG_COLS + (t % NB) * GT_A_COLS;
+                    if (!expired && !mbar_wait_bounded(afull(is, t % NB), (t / NB) & 1)) expired = true;
+                    // one accumulator set: the generating warps must have read the finished chain
+                    if (SETS == 1 && head && t > 0 && !expired && !mbar_wait_bounded(dfree(is), (t / GT_CHAIN - 1) & 1)) expired = true;
+                    tc::fence_after_sync();
                     {
-                        if (!expired && !mbar_wait_bounded(afull(is, t % NB), (t / NB) & 1)) expired = true;
-                        if (SETS == 1 && head && t > 0 && !expired && !mbar_wait_bounded(dfree(is), (t / GT_CHAIN - 1) & 1)) expired = true;
-                        tc::fence_after_sync();
-                       
-                    }
-                    {
-                        
-// Every MMA of this shape holds the tensor pipe for the same ~45 cycles whatever its
-                        // width up to 64 columns; consecutive ones go to different accumulator columns.
+                        // Every MMA of this shape holds the tensor pipe for the same ~45 cycles whatever its width
+                        // up to 64 columns (64 cycles at 128); consecutive ones go to different accumulator columns.
 #pragma unroll
                         for (int rg = 0; rg < RG_PER; ++rg)
                             tc::mma_tf32_a_tmem(d0 + rg * S::RG_COLS, a0 + rg * S::RG_COLS, db0, idesc_main, !head);
@@ -400,7 +390,6 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
                     tc::commit(aempty(t % NB));
                     if (tail) tc::commit(dfull(set));
                     if (hf == 1) tc::commit(cfree(slot));
-                   
                 }
             }
         }
