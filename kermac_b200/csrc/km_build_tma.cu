@@ -184,6 +184,26 @@ int encode_operand(CUtensorMap* map, const float* base, int extent, int K, int L
     return 0;
 }
 
+int encode_box(CUtensorMap* map, const float* base, int inner, int outer, int L, long long s_outer, long long s_l,
+               int box_inner, int box_outer) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(KM_ERR_INTERNAL, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t row_bytes = (static_cast<cuuint64_t>(inner) * 4 + 15) & ~static_cast<cuuint64_t>(15);
+    const int        oo        = outer > 0 ? outer : 1;
+    const int        ll        = (s_l == 0) ? 1 : L;
+    cuuint64_t stride_o        = (oo > 1) ? static_cast<cuuint64_t>(s_outer) * 4 : row_bytes;
+    cuuint64_t stride_l        = (ll > 1) ? static_cast<cuuint64_t>(s_l) * 4 : stride_o * oo;
+    cuuint64_t dims[3]         = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(oo), static_cast<cuuint64_t>(ll)};
+    cuuint64_t strides[2]      = {stride_o, stride_l};
+    cuuint32_t box[3]          = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer), 1};
+    cuuint32_t estr[3]         = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(KM_ERR_INTERNAL, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return 0;
+}
+
 bool operand_tma_ok(const float* base, long long s_t, long long s_k, long long s_l, int K, int L) {
     if (s_t != 1 || !aligned16(base)) return false;
     if (K > 1 && (s_k % 4 != 0 || s_k <= 0 || s_k >= (1LL << 36))) return false;
@@ -234,6 +254,10 @@ TmaChoice tma_kernel(int inner) {
 int encode_tma_operand(CUtensorMap* map, const float* base, int extent, int K, int L, long long s_k, long long s_l,
                        int box_k) {
     return encode_operand(map, base, extent, K, L, s_k, s_l, box_k);
+}
+int encode_tma_box(CUtensorMap* map, const float* base, int inner, int outer, int L, long long s_outer, long long s_l,
+                   int box_inner, int box_outer) {
+    return encode_box(map, base, inner, outer, L, s_outer, s_l, box_inner, box_outer);
 }
 bool tma_operand_ok(const float* base, long long s_t, long long s_k, long long s_l, int K, int L) {
     return operand_tma_ok(base, s_t, s_k, s_l, K, L);

@@ -45,6 +45,9 @@
 // flag (kermac_b200_device_error_flag) and lets the block run to its end without its results.  (Spinning
 // on the non-blocking mbarrier test instead of the suspending try_wait measured 1 % slower and tripled
 // the instructions executed.)
+#include <cstring>
+
+#include "km_build_tma.cuh"
 #include "km_common.cuh"
 #include "km_host.h"
 #include "km_mbar.cuh"
@@ -105,12 +108,19 @@ __device__ __forceinline__ void generators_barrier() { asm volatile("bar.sync 1,
 
 
 // 16 weights of one (n, m) row: k = 0..15 of arow (a transposed) and brow, split into hi / lo.
-template <int NORM, bool TAIL>
+// A_STRIDE: floats between consecutive k of the a operand (1: staged transposed, read 16 bytes at a time).
+template <int NORM, bool TAIL, int A_STRIDE>
 __device__ __forceinline__ void weights16(uint32_t (&hi)[16], uint32_t (&lo)[16], const float* arow, const float* brow,
                                           u64 dd, float pm1, int kvalid) {
 #pragma unroll
     for (int q4 = 0; q4 < 4; ++q4) {
-        const ulonglong2 a4 = *reinterpret_cast<const ulonglong2*>(arow + 4 * q4);
+        ulonglong2 a4;
+        if constexpr (A_STRIDE == 1) {
+            a4 = *reinterpret_cast<const ulonglong2*>(arow + 4 * q4);
+        } else {
+            a4.x = pack2(arow[(4 * q4) * A_STRIDE], arow[(4 * q4 + 1) * A_STRIDE]);
+            a4.y = pack2(arow[(4 * q4 + 2) * A_STRIDE], arow[(4 * q4 + 3) * A_STRIDE]);
+        }
         const ulonglong2 b4 = *reinterpret_cast<const ulonglong2*>(brow + 4 * q4);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -147,13 +157,20 @@ __device__ __forceinline__ void weights16(uint32_t (&hi)[16], uint32_t (&lo)[16]
     }
 }
 
-template <int NORM, int OT, int RG>
-__global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLOCKS_PER_SM) grad_tensor_kernel(const __grid_constant__ GradTensorParams p) {
+// TMA: a and b staged by tiled TMA copies (no multicast) into a ring with a full and an empty mbarrier per
+// stage, each stage refilled by the warp whose arrival completes its empty phase: no per-thread copies, no
+// block barrier, the warps drift apart freely.  a then sits in shared memory as it does in global memory
+// ([k][m]) and is read one float at a time.  Otherwise: 4-byte cp.async copies (any alignment), a transposed.
+template <int NORM, int OT, int RG, bool TMA>
+__global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLOCKS_PER_SM)
+grad_tensor_kernel(const __grid_constant__ GradTensorParams p, const __grid_constant__ CUtensorMap map_a,
+                   const __grid_constant__ CUtensorMap map_b) {
     using S = GtShape<OT, RG>;
     extern __shared__ unsigned char smem_raw[];
     // afull[rg][buf] (one arrival per generating warp of the row group), aempty[buf], dfull[set], cfree[slot]
     // (tcgen05.commit), cfull[slot] (the coefficient warp)
     __shared__ __align__(8) unsigned long long s_bars[S::ISSUERS * S::A_BUFS + S::A_BUFS + 2 + 2 * GT_C_SLOTS + S::ISSUERS];
+    __shared__ __align__(8) unsigned long long s_ring[2 * GT_STAGES];   // full[stage], empty[stage] (TMA staging)
     __shared__ uint32_t s_tmem;
 
     const uint32_t raw_addr = smem_u32(smem_raw);
@@ -203,7 +220,14 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
             mbar_init(cfull(sl), S::C_WARPS);
             mbar_init(cfree(sl), NI);
         }
+        if constexpr (TMA) {
+            for (int st = 0; st < GT_STAGES; ++st) {
+                mbar_init(smem_u32(s_ring) + 8u * st, 1);
+                mbar_init(smem_u32(s_ring) + 8u * (GT_STAGES + st), S::GEN_WARPS);
+            }
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        tc::fence_smem_to_async();
     }
     if (warp == S::GEN_WARPS) tc::tmem_alloc(smem_u32(&s_tmem), S::TMEM_COLS);
     tc::fence_before_sync();
@@ -259,6 +283,7 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
         const uint32_t stages_addr = smem_u32(stages);
 
         auto stage = [&](int s) {
+            if constexpr (TMA) return;
             const uint32_t base = stages_addr + (s % GT_STAGES) * (S::STAGE_FLOATS * 4);
             const int krem      = k_end - (k_begin + s * GT_BK);        // k rows of this slab that exist
             const long long ks  = (long long)s * GT_BK;
@@ -270,6 +295,19 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
             const bool ok = b_ok && b_kk < krem;
             cp_async_4(base + b_dst, ok ? b_src + ks : p.B, ok ? 4 : 0);
         };
+        // TMA staging: one thread asks for a slab's two boxes; the stage's full barrier receives the bytes
+        const uint32_t ring = smem_u32(s_ring);
+        auto full_bar  = [&](int st) { return ring + 8u * st; };
+        auto empty_bar = [&](int st) { return ring + 8u * (GT_STAGES + st); };
+        const int la = (p.a_sl == 0) ? 0 : l, lb = (p.b_sl == 0) ? 0 : l;   // a broadcast operand has one batch slice
+        auto issue = [&](int s) {
+            const int st       = s % GT_STAGES;
+            const uint32_t dst = stages_addr + st * (S::STAGE_FLOATS * 4);
+            mbar_expect_tx(full_bar(st), (GT_TM + S::TN) * GT_BK * 4);
+            tma_load_3d(dst, &map_a, m0, k_begin + s * GT_BK, la, full_bar(st));
+            tma_load_3d(dst + GT_TM * GT_BK * 4, &map_b, k_begin + s * GT_BK, n0, lb, full_bar(st));
+        };
+        int fail_s = -1;                               // first slab whose wait ran out on this thread
         auto drain = [&](int c) {
             const int set = SETS == 2 ? (c & 1) : 0;
             if (!expired && !mbar_wait_bounded(dfull(set), (SETS == 2 ? (c >> 1) : c) & 1)) expired = true;
@@ -298,27 +336,52 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
             if (lane == 0) mbar_arrive(afull(rg / RG_PER, t % NB));
         };
 
+        if constexpr (TMA) {
+            if (tid == 0)
+                for (int s = 0; s < GT_STAGES && s < nslabs; ++s) issue(s);
+        } else {
 #pragma unroll
-        for (int s = 0; s < GT_STAGES - 1; ++s) {
-            if (s < nslabs) stage(s);
-            cp_async_commit();
+            for (int s = 0; s < GT_STAGES - 1; ++s) {
+                if (s < nslabs) stage(s);
+                cp_async_commit();
+            }
         }
         int next_drain = 0;
         for (int s = 0; s < nslabs; ++s) {
-            cp_async_wait<GT_STAGES - 2>();
-            generators_barrier<S::GEN_THREADS>();
-            if (s + GT_STAGES - 1 < nslabs) stage(s + GT_STAGES - 1);
-            cp_async_commit();
-            const float* sa  = stages + (s % GT_STAGES) * S::STAGE_FLOATS + mm * GT_PA;
-            const float* sb  = stages + (s % GT_STAGES) * S::STAGE_FLOATS + GT_TM * GT_PA + nn * GT_PB;
+            if constexpr (TMA) {
+                if (!expired && !mbar_wait_bounded(full_bar(s % GT_STAGES), (s / GT_STAGES) & 1)) {
+                    expired = true;
+                    fail_s  = s;
+                }
+            } else {
+                cp_async_wait<GT_STAGES - 2>();
+                generators_barrier<S::GEN_THREADS>();
+                if (s + GT_STAGES - 1 < nslabs) stage(s + GT_STAGES - 1);
+                cp_async_commit();
+            }
+            constexpr int A_STRIDE = TMA ? GT_TM : 1;
+            const float* sa  = stages + (s % GT_STAGES) * S::STAGE_FLOATS + (TMA ? mm : mm * GT_PA);
+            const float* sb  = stages + (s % GT_STAGES) * S::STAGE_FLOATS + (TMA ? GT_TM * GT_BK + nn * GT_BK : GT_TM * GT_PA + nn * GT_PB);
             const int kvalid = k_end - (k_begin + s * GT_BK);
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
                 const int t = 2 * s + hf;
                 uint32_t hi[16], lo[16];
                 // computed while the tensor-memory stores of the step before are still in flight
-                if (kvalid >= GT_BK) weights16<NORM, false>(hi, lo, sa + hf * GT_KA, sb + hf * GT_KA, dd, pm1, GT_KA);
-                else                 weights16<NORM, true>(hi, lo, sa + hf * GT_KA, sb + hf * GT_KA, dd, pm1, kvalid - hf * GT_KA);
+                if (kvalid >= GT_BK)
+                    weights16<NORM, false, A_STRIDE>(hi, lo, sa + hf * GT_KA * A_STRIDE, sb + hf * GT_KA, dd, pm1, GT_KA);
+                else
+                    weights16<NORM, true, A_STRIDE>(hi, lo, sa + hf * GT_KA * A_STRIDE, sb + hf * GT_KA, dd, pm1, kvalid - hf * GT_KA);
+                if constexpr (TMA) {
+                    if (hf == 1) {
+                        // the slab is in registers: the arrival that completes the stage's empty phase refills it
+                        __syncwarp();
+                        if (lane == 0 && mbar_arrive_pending(empty_bar(s % GT_STAGES)) == 1 && s + GT_STAGES < nslabs && !expired) {
+                            mbar_try_wait(empty_bar(s % GT_STAGES), (s / GT_STAGES) & 1);   // the acquire side of the hand-over
+                            issue(s + GT_STAGES);
+                        }
+                    }
+                }
                 if (t > 0) publish(t - 1);
                 // the chain before the running one finished a buffer ago: add it to the running sums
                 // (with a single accumulator set: at the first step of the next chain, which cannot start before)
@@ -335,6 +398,17 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
             }
         }
         cp_async_wait<0>();
+        if constexpr (TMA) {
+            // give copies already handed to the TMA engine a bounded chance to land before the block's shared
+            // memory is released
+            if (expired && lane == 0) {
+                const int first = fail_s < 0 ? 0 : fail_s;
+                const int last  = first + GT_STAGES < nslabs ? first + GT_STAGES : nslabs;
+                for (int slab = first; slab < last; ++slab)
+                    for (int i = 0; i < (1 << 16); ++i)
+                        if (mbar_try_wait(full_bar(slab % GT_STAGES), (slab / GT_STAGES) & 1)) break;
+            }
+        }
         if (T > 0) publish(T - 1);
         while (next_drain < chains) {
             drain(next_drain);
@@ -464,15 +538,15 @@ __global__ void __launch_bounds__(GtShape<OT, RG>::THREADS, GtShape<OT, RG>::BLO
     if (warp == S::GEN_WARPS) tc::tmem_dealloc(tmem, S::TMEM_COLS);
 }
 
-typedef void (*GradTensorFn)(const GradTensorParams);
+typedef void (*GradTensorFn)(const GradTensorParams, const CUtensorMap, const CUtensorMap);
 
-template <int OT, int RG>
+template <int OT, int RG, bool TMA>
 GradTensorFn grad_tensor_fn(int norm_kind) {
     switch (norm_kind) {
-        case KM_NORM_L1: return grad_tensor_kernel<KM_NORM_L1, OT, RG>;
-        case KM_NORM_L2: return grad_tensor_kernel<KM_NORM_L2, OT, RG>;
-        case KM_NORM_P: return grad_tensor_kernel<KM_NORM_P, OT, RG>;
-        case GT_NORM_SQRT: return grad_tensor_kernel<GT_NORM_SQRT, OT, RG>;
+        case KM_NORM_L1: return grad_tensor_kernel<KM_NORM_L1, OT, RG, TMA>;
+        case KM_NORM_L2: return grad_tensor_kernel<KM_NORM_L2, OT, RG, TMA>;
+        case KM_NORM_P: return grad_tensor_kernel<KM_NORM_P, OT, RG, TMA>;
+        case GT_NORM_SQRT: return grad_tensor_kernel<GT_NORM_SQRT, OT, RG, TMA>;
     }
     return nullptr;
 }
@@ -480,13 +554,26 @@ GradTensorFn grad_tensor_fn(int norm_kind) {
 template <int OT, int RG>
 int grad_tensor_launch_shape(const GradTensorParams& p, int norm_kind, cudaStream_t st) {
     using S = GtShape<OT, RG>;
-    GradTensorFn fn = grad_tensor_fn<OT, RG>(norm_kind);
+    // tiled TMA copies need 16-byte aligned bases and pitches that are multiples of 16 bytes
+#ifndef GT_NO_TMA
+    const bool tma = tma_operand_ok(p.A, 1, p.lda, p.a_sl, p.K, p.L) && tma_operand_ok(p.B, 1, p.ldb, p.b_sl, p.N, p.L);
+#else
+    const bool tma = false;
+#endif
+    GradTensorFn fn = tma ? grad_tensor_fn<OT, RG, true>(norm_kind) : grad_tensor_fn<OT, RG, false>(norm_kind);
+    CUtensorMap map_a, map_b;
+    memset(&map_a, 0, sizeof(map_a));
+    memset(&map_b, 0, sizeof(map_b));
+    if (tma) {
+        if (int rc = encode_tma_box(&map_a, p.A, p.M, p.K, p.L, p.lda, p.a_sl, GT_TM, GT_BK)) return rc;
+        if (int rc = encode_tma_box(&map_b, p.B, p.K, p.N, p.L, p.ldb, p.b_sl, GT_BK, S::TN)) return rc;
+    }
     if (!fn) return fail(KM_ERR_INTERNAL, "no tensor-core gradient kernel for norm kind %d", norm_kind);
     if (int rc = cuda_status(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES),
                              "cudaFuncSetAttribute(grad_tensor_kernel)"))
         return rc;
     dim3 grid((unsigned)((long long)p.tiles_m * p.tiles_n * p.splits), (unsigned)p.o_chunks, (unsigned)p.L);
-    fn<<<grid, S::THREADS, S::SMEM_BYTES, st>>>(p);
+    fn<<<grid, S::THREADS, S::SMEM_BYTES, st>>>(p, map_a, map_b);
     return cuda_status(cudaGetLastError(), "launch of grad_tensor_kernel");
 }
 

@@ -67,6 +67,24 @@ def test_odd_shapes_and_unaligned_views(shape):
     clean_flag()
 
 
+@pytest.mark.parametrize("shape", [(36, 44, 21, 20), (4, 8, 3, 16), (260, 100, 37, 40), (1000, 64, 16, 64)])
+def test_tma_staging_and_copy_staging_give_the_same_bits(shape):
+    # operands with 16-byte aligned rows are staged by TMA, anything else by 4-byte copies: the arithmetic and
+    # its order are the same, so the same numbers behind an unaligned view must give the same bits
+    K, M, N, O = shape
+    a, b, c, d = gen((K, M), 45, "rand").cuda(), gen((N, K), 46).cuda(), gen((O, K), 47).cuda(), gen((N, M), 48).cuda()
+    a_view = torch.zeros(K, M + 3, device="cuda")[:, 1:M + 1]
+    b_view = torch.zeros(N, K + 1, device="cuda")[:, :K]
+    a_view.copy_(a)
+    b_view.copy_(b)
+    for p in (1.0, 2.0, 1.7):
+        aligned = kermac.cdist_grad(a, b, c, d, p=p, contraction="tensor")
+        views = kermac.cdist_grad(a_view, b_view, c, d, p=p, contraction="tensor")
+        assert torch.equal(aligned, views)
+        assert ko.rel_err_signed(aligned, ko.cdist_grad_ref(a.cpu(), b.cpu(), c.cpu(), d.cpu(), p=p)) < TOL
+    clean_flag()
+
+
 def test_exact_ties_follow_copysign():
     # d[n, m] == b[n, k] for many triples: p = 1 counts them as +1, p > 1 as 0, as the FP32 kernel does
     K, M, N, O = 48, 64, 8, 16
