@@ -56,7 +56,7 @@
 namespace km {
 namespace {
 
-constexpr int GT_STAGES  = 3;               // staged slabs of GT_BK k rows
+constexpr int GT_STAGES  = 3;               // staged slabs of GT_BK k rows (five are no faster)
 constexpr int GT_PA      = GT_BK + 4;       // floats per staged row of a (transposed: [m][k])
 constexpr int GT_PB      = GT_BK + 8;       // floats per staged row of b ([n][k])
 constexpr int GT_KA      = 16;              // k per tensor-memory A buffer
@@ -86,8 +86,8 @@ struct GtShape {
     // A buffers per accumulator chain (128 k).  Twice as long saves 5 % at 64 channels (34.6 against 36.5 ms) and
     // doubles the drift of same-sign sums (2.0e-6 against 1.1e-6 of the result over 20000 terms).
     static constexpr int CHAIN        = 8;
-    // A buffers of 16 k per row group.  Four of them (at two row groups) measured slower than two:
-    // 33.8 against 28.9 ms at 32 channels.
+    // A buffers of 16 k per row group.  Four of them (at two row groups) are no faster than two: 28.0 against
+    // 27.5 ms at 32 channels, 32.3 against 33.1 at 64.
     static constexpr int A_BUFS       = 2;
     static constexpr int D_OFF        = A_BUFS * GT_A_COLS;        // accumulator sets start after the A buffers
     static constexpr int RG_COLS      = D_OFF + SETS * D_COLS;     // tensor-memory columns per row group
@@ -328,7 +328,8 @@ grad_tensor_kernel(const __grid_constant__ GradTensorParams p, const __grid_cons
                 if (lane == 0) mbar_arrive(dfree(rg / RG_PER));
             }
         };
-        // hands the A buffer of step t to the MMA warp, once its tensor-memory stores have landed
+        // hands the A buffer of step t to the MMA warp, once its tensor-memory stores have landed (putting the
+        // next step's weights between the stores and this wait measured slower: 20.6 against 19.1 ms at 16 channels)
         auto publish = [&](int t) {
             tc::wait_st();
             tc::fence_before_sync();
@@ -367,7 +368,6 @@ grad_tensor_kernel(const __grid_constant__ GradTensorParams p, const __grid_cons
             for (int hf = 0; hf < 2; ++hf) {
                 const int t = 2 * s + hf;
                 uint32_t hi[16], lo[16];
-                // computed while the tensor-memory stores of the step before are still in flight
                 if (kvalid >= GT_BK)
                     weights16<NORM, false, A_STRIDE>(hi, lo, sa + hf * GT_KA * A_STRIDE, sb + hf * GT_KA, dd, pm1, GT_KA);
                 else
@@ -382,7 +382,6 @@ grad_tensor_kernel(const __grid_constant__ GradTensorParams p, const __grid_cons
                         }
                     }
                 }
-                if (t > 0) publish(t - 1);
                 // the chain before the running one finished a buffer ago: add it to the running sums
                 // (with a single accumulator set: at the first step of the next chain, which cannot start before)
                 if (t == GT_CHAIN * next_drain + GT_CHAIN + (SETS == 2 ? 1 : 0)) {
@@ -395,6 +394,7 @@ grad_tensor_kernel(const __grid_constant__ GradTensorParams p, const __grid_cons
                 tc::fence_after_sync();
                 tc::st_32x32b_x16(t_row + (t % NB) * GT_A_COLS, hi);
                 tc::st_32x32b_x16(t_row + (t % NB) * GT_A_COLS + GT_KA, lo);
+                publish(t);
             }
         }
         cp_async_wait<0>();
@@ -409,7 +409,6 @@ grad_tensor_kernel(const __grid_constant__ GradTensorParams p, const __grid_cons
                         if (mbar_try_wait(full_bar(slab % GT_STAGES), (slab / GT_STAGES) & 1)) break;
             }
         }
-        if (T > 0) publish(T - 1);
         while (next_drain < chains) {
             drain(next_drain);
             ++next_drain;
