@@ -439,9 +439,9 @@ int make_grad_plan(const KmGradArgs* a, GradPlan* plan) {
     while (ot < a->o && ot < 16) ot *= 2;
     // The tensor-core kernel forms each weight once for up to 64 channels and leaves the channel
     // products to the MMA.  Up to 16 channels the FP32 kernel is level or faster (K = 30000, M = 4096,
-    // N = 256: 20.4 against 22.4 ms at 16); from 17 on it needs a second pass and the tensor cores
-    // win (40.4 against 28.0 ms at 32, 80.7 against 36.7 at 64).  The tensor kernel needs at least one
-    // slab of k.
+    // N = 256: 20.4 against 19.1 ms at 16, 20.3 when the operands cannot be staged by TMA); from 17 on
+    // it needs a second pass and the tensor cores win (40.4 against 23.1 ms at 32, 80.7 against 29.6 at
+    // 64).  The tensor kernel needs at least one slab of k.
     plan->tensor = a->k > 0 && (a->contraction == KM_CONTRACT_TENSOR ||
                                 (a->contraction == KM_CONTRACT_AUTO && a->o >= KM_GRAD_TENSOR_MIN_O && a->k >= 8 * G_BK));
     if (plan->tensor) ot = gt_ot_for(a->o);

@@ -28,18 +28,19 @@
 // lanes), two warps issue the MMAs (half of the row groups each), one or two warps split and park the
 // coefficients.  Per row group tensor memory holds two A buffers of 16 k (hi and lo: 2 x 32 columns)
 // and the accumulators (2 OT columns per set); the block allocates all 512 columns of its SM and runs
-// alone there: OT = 16 with 4 row groups (16 n) and OT = 32 with 2 (8 n), two accumulator sets each;
-// OT = 64 with 2 row groups and one accumulator set (the next chain's MMAs wait until the generating
-// warps have read the finished one).
+// alone there: OT = 16 with 4 row groups (16 n) and two accumulator sets; OT = 32 with 4 row groups and
+// OT = 64 with 2 (8 n), one accumulator set each (the next chain's MMAs wait until the generating warps
+// have read the finished one).
 //
-// What bounds it (B200, K = 30000, M = 4096, N = 256, p = 1: 22.4 ms at 16 channels, 28.0 at 32, 36.7
+// What bounds it (B200, K = 30000, M = 4096, N = 256, p = 1: 19.1 ms at 16 channels, 23.1 at 32, 29.6
 // at 64, against 20.4 / 40.4 / 80.7 ms of the FP32 kernel): a tcgen05.mma kind::tf32 of 128 rows x 8 k
 // holds the tensor pipe for max(45, N / 2) cycles whatever its width N, so the narrow MMAs of this product
-// run the pipe at a quarter (N = 32) or half (N = 64) of its rate: 9.5 ms of MMAs per pass alone.  At 16
-// channels the weight generation (11 ms alone), the tensor-memory stores (+5 to 8 ms) and the MMAs (+4 to
-// 7 ms) overlap only in part: tensor memory has room for two A buffers per row group, and the registers
-// for no more than ~20 warps.  Hence the automatic choice: tensor cores from 17 channels on, where the
-// FP32 kernel needs a second pass.
+// run the pipe at a quarter (N = 32) or half (N = 64) of its rate: 9.5 ms of MMAs per pass alone.  The
+// weight generation, the tensor-memory stores and the MMAs of a step hang on one another (with the copy
+// staging at 16 channels: 11 ms for the generation alone, +5 to 8 with the stores, +4 to 7 with the MMAs)
+// and overlap only in part: tensor memory has room for two A buffers per row group, and the registers for
+// no more than ~20 warps.  The automatic choice takes the tensor cores from 17 channels on, where the FP32
+// kernel needs a second pass.
 //
 // Hand-over between the warps is by mbarriers; every wait is bounded, and a wait that runs out sets a
 // flag (kermac_b200_device_error_flag) and lets the block run to its end without its results.  (Spinning
@@ -80,9 +81,10 @@ struct GtShape {
     static constexpr int C_BYTES      = 2 * OT * 128;              // 2 OT rows (c_hi, c_lo) of 32 k
     static constexpr int D_COLS       = 2 * OT;                    // one accumulator set: main, correction
     // Accumulator sets per row group.  Two alternate, so that a finished chain is added up while the next one
-    // runs; at 64 channels tensor memory has room for one, and the MMAs of the next chain wait for the
-    // generating warps to have read the finished one.
-    static constexpr int SETS         = OT >= 64 ? 1 : 2;
+    // runs, where tensor memory has room for them (16 channels); otherwise there is one, and the MMAs of the
+    // next chain wait for the generating warps to have read the finished one.  (32 channels with two row groups
+    // and two sets: 26.9 ms; with four row groups and one set, i.e. twice the generating warps: 23.1.)
+    static constexpr int SETS         = RG * (2 * GT_A_COLS + 2 * D_COLS) <= 512 ? 2 : 1;
     // A buffers per accumulator chain (128 k).  Twice as long saves 5 % at 64 channels (34.6 against 36.5 ms) and
     // doubles the drift of same-sign sums (2.0e-6 against 1.1e-6 of the result over 20000 terms).
     static constexpr int CHAIN        = 8;
@@ -580,15 +582,15 @@ int grad_tensor_launch_shape(const GradTensorParams& p, int norm_kind, cudaStrea
 
 int grad_tensor_launch(const GradTensorParams& p, int norm_kind, cudaStream_t st) {
     if (p.ot == 16 && p.rg == 4) return grad_tensor_launch_shape<16, 4>(p, norm_kind, st);
-    if (p.ot == 32 && p.rg == 2) return grad_tensor_launch_shape<32, 2>(p, norm_kind, st);
+    if (p.ot == 32 && p.rg == 4) return grad_tensor_launch_shape<32, 4>(p, norm_kind, st);
     if (p.ot == 64 && p.rg == 2) return grad_tensor_launch_shape<64, 2>(p, norm_kind, st);
     return fail(KM_ERR_INTERNAL, "no tensor-core gradient kernel for %d channels x %d row groups per block", p.ot, p.rg);
 }
 
 // Row groups per block: as many as tensor memory holds (two A buffers of 32 columns and two accumulator
 // sets of 2 OT columns per row group).
-int gt_rg_for(int ot) { return ot >= 32 ? 2 : 4; }
-int gt_blocks_per_sm(int ot) { return ot == 64 ? GtShape<64, 2>::BLOCKS_PER_SM : ot == 32 ? GtShape<32, 2>::BLOCKS_PER_SM : GtShape<16, 4>::BLOCKS_PER_SM; }
+int gt_rg_for(int ot) { return ot == 64 ? 2 : 4; }
+int gt_blocks_per_sm(int ot) { return ot == 64 ? GtShape<64, 2>::BLOCKS_PER_SM : ot == 32 ? GtShape<32, 4>::BLOCKS_PER_SM : GtShape<16, 4>::BLOCKS_PER_SM; }
 
 int grad_tensor_take_wait_flag() {
     int v = 0, zero = 0;

@@ -34,7 +34,7 @@ constexpr int GT_TM = 32;          // m per thread block
 constexpr int GT_BK = 32;          // k rows per staged slab; k ranges of a split are multiples of it
 // Channels per thread block: 16, 32 or 64, the smallest that holds them all (an MMA of up to 64 output
 // columns holds the tensor pipe as long as one of 16, one of 128 only 1.4 times as long); n rows per thread
-// block that go with it (tensor memory holds four row groups of 128 pairs at 16 channels, two at 32 and 64).
+// block that go with it (tensor memory holds four row groups of 128 pairs at 16 and 32 channels, two at 64).
 inline int gt_ot_for(int o) { return o > 32 ? 64 : (o > 16 ? 32 : 16); }
 int gt_rg_for(int ot);                                 // row groups of 128 pairs per thread block
 inline int gt_tn_for(int ot) { return 4 * gt_rg_for(ot); }
