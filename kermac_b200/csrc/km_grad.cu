@@ -440,7 +440,7 @@ int make_grad_plan(const KmGradArgs* a, GradPlan* plan) {
     // The tensor-core kernel forms each weight once for up to 64 channels and leaves the channel
     // products to the MMA.  Up to 16 channels the FP32 kernel is level or faster (K = 30000, M = 4096,
     // N = 256: 20.4 against 19.1 ms at 16, 20.3 when the operands cannot be staged by TMA); from 17 on
-    // it needs a second pass and the tensor cores win (40.4 against 23.1 ms at 32, 80.7 against 29.6 at
+    // it needs a second pass and the tensor cores win (40.4 against 22.0 ms at 32, 80.7 against 29.6 at
     // 64).  The tensor kernel needs at least one slab of k.
     plan->tensor = a->k > 0 && (a->contraction == KM_CONTRACT_TENSOR ||
                                 (a->contraction == KM_CONTRACT_AUTO && a->o >= KM_GRAD_TENSOR_MIN_O && a->k >= 8 * G_BK));

@@ -32,7 +32,7 @@
 // OT = 64 with 2 (8 n), one accumulator set each (the next chain's MMAs wait until the generating warps
 // have read the finished one).
 //
-// What bounds it (B200, K = 30000, M = 4096, N = 256, p = 1: 19.1 ms at 16 channels, 23.1 at 32, 29.6
+// What bounds it (B200, K = 30000, M = 4096, N = 256, p = 1: 19.1 ms at 16 channels, 22.0 at 32, 29.6
 // at 64, against 20.4 / 40.4 / 80.7 ms of the FP32 kernel): a tcgen05.mma kind::tf32 of 128 rows x 8 k
 // holds the tensor pipe for max(45, N / 2) cycles whatever its width N, so the narrow MMAs of this product
 // run the pipe at a quarter (N = 32) or half (N = 64) of its rate: 9.5 ms of MMAs per pass alone.  The
@@ -72,9 +72,10 @@ struct GtShape {
     static constexpr int GEN_WARPS    = 4 * RG;
     static constexpr int GEN_THREADS  = 32 * GEN_WARPS;
     static constexpr int ISSUERS      = RG >= 2 ? 2 : 1;           // warps that issue MMAs, RG / ISSUERS row groups each
-    // warps that park the coefficients: one was the slowest warp of the block from 32 channels on (64 channels:
-    // 48.3 ms with one, 36.7 with two; four cost registers the generating warps need: 40.6)
-    static constexpr int C_WARPS      = OT >= 32 ? 2 : 1;
+    // warps that park the coefficients: at 64 channels one was the slowest warp of the block (48.3 ms with one,
+    // 36.7 with two; four cost registers the generating warps need: 40.6); at 32 channels on four row groups
+    // one is enough and a second only competes with the generating warps (22.0 against 23.0 ms)
+    static constexpr int C_WARPS      = OT >= 64 ? 2 : 1;
     static constexpr int THREADS      = GEN_THREADS + 32 * (ISSUERS + C_WARPS);   // + the MMA warps and the coefficient warps
     static constexpr int TN           = 4 * RG;                    // n rows of the tile
     static constexpr int STAGE_FLOATS = GT_TM * GT_PA + TN * GT_PB;
